@@ -120,18 +120,24 @@ enum b200_ext_op {
     B200_EXT_LATENT_ATTN = 7,  /* src: q_lat, q_rot, cache, sink, tok_seq, tok_pos, cell_seq, cell_pos; op_params: [2] kv_rank, [3] scale, [4] window */
     B200_EXT_MLSTM_SCAN = 8,   /* src: q, k, v, ig, fg, i_bias, f_bias, seq_info, state; op_params: [2] heads, [3] dim, [4] vdim, [5] gate_cap */
     B200_EXT_QKV_STORE = 9,    /* src: q, k, v, vecs (the present ones of q.b, k.b, v.b, q.norm, k.norm packed in one tensor, or NULL), pos, freqs,
-                                  cells, k cache, v cache; q in place; op_params: [2] dim, [3] vdim, [4] n_dims, [5] eps, [6] biases present, [7] norms present */
-    B200_EXT_SINK_ATTN = 10,   /* src: q, k cache, v cache, sink, tok_seq, tok_pos, cell_seq, cell_pos; op_params: [2] dim, [3] scale, [4] window,
-                                  [5] keep_first, [6] bf16 products, [7] vdim */
+                                  cells, k cache, v cache; q in place; op_params: [2] dim, [3] vdim, [4] n_dims, [5] eps, [6] biases present, [7] norms present
+                                  (1: over the whole row, 2: per head with one weight vector of dim values), [8] pairs are (i, i + n_dims / 2) */
+    B200_EXT_SINK_ATTN = 10,   /* src: q, k cache, v cache, sink, tok_seq, tok_pos, cell_seq, cell_pos, [head gate [heads, T]]; op_params: [2] dim, [3] scale,
+                                  [4] window, [5] keep_first, [6] bf16 products, [7] vdim, [8] chunk */
     B200_EXT_LINEAR_ATTN_SCAN = 11, /* src: q, k, v, decay, seq_info, state; op_params: [2] heads, [3] dim, [4] vdim, [5] silu on q / k / v */
     B200_EXT_MOE_ROUTE = 12,   /* src: logits, correction; dst [2 n_used, T]: per token n_used weights (f32), then n_used expert ids (i32);
-                                  op_params: [2] n_group, [3] n_group_used, [4] scale, [5] n_used */
-    B200_EXT_SILU_MUL = 13,    /* src: a, b: dst = silu(a) * b, any strides */
+                                  op_params: [2] n_group, [3] n_group_used, [4] scale, [5] n_used, [6] enum b200_router_score, [7] weights are the
+                                  scores as they are (no division by their sum) */
+    B200_EXT_SILU_MUL = 13,    /* src: a, b: dst = act(a) * b, any strides; op_params: [2] enum b200_glu_kind (0: silu), [3] limit, [4] alpha */
     B200_EXT_MOE_COMBINE = 14, /* src: y [n, n_used, T], weights [n_used, T], add0, add1 (optional [n, T]): dst = add0 + add1 + sum_k w_k y_k */
     B200_EXT_UNARY = 15,       /* src: x; op_params: [2] enum b200_unary_op, [3] p0, [4] p1 */
     B200_EXT_MUL_MAT_ID = 16,  /* src: experts [K, M, E] f32 / bf16, b [K, n_b_rows, T], ids [n_used, T]: dense-weight form of MUL_MAT_ID */
 };
 
+enum b200_router_score { B200_ROUTER_SIGMOID = 0, B200_ROUTER_SOFTMAX = 1 /* over all experts */ };
+/* gated activations dst = f(a, b): SILU a sigmoid(a) b; GELU_TANH gelu(a) b with the tanh form of gelu; SWISH_CLAMPED with g = min(a, limit),
+ * u = clamp(b, -limit, limit): g sigmoid(alpha g) (u + 1) */
+enum b200_glu_kind { B200_GLU_SILU = 0, B200_GLU_GELU_TANH = 1, B200_GLU_SWISH_CLAMPED = 2 };
 enum b200_norm_kind { B200_NORM_LAYER = 0 /* (x - mean) / sqrt(var + eps) */, B200_NORM_RMS = 1 /* x / sqrt(mean(x^2) + eps) */ };
 
 /* dst[row] = (res ? res[row] : 0) + N(x[row] * (gate ? sigmoid(gate[row] + gate_bias) : 1)) * w[(row % w_period)], N the layer
@@ -209,13 +215,16 @@ B200_API int b200_op_mlstm_scan(const b200_mlstm_args *a, b200_stream_t stream);
 
 /* dst = silu(a) * b; a, b, dst f32 of one shape with any strides (the two halves of a fused gate / up product are fine). */
 B200_API int b200_op_silu_mul_strided(const b200_tensor *a, const b200_tensor *b, const b200_tensor *dst, b200_stream_t stream);
+/* The same for any enum b200_glu_kind; limit and alpha are read by B200_GLU_SWISH_CLAMPED only. */
+B200_API int b200_op_glu_strided(int kind, const b200_tensor *a, const b200_tensor *b, const b200_tensor *dst, float limit, float alpha, b200_stream_t stream);
 
 /* Softmax attention of n_head query heads over cached keys and values of n_head_kv heads (query head h reads kv head
  * h / (n_head / n_head_kv)); one cache row per cell holds all kv heads of a token: k rows [n_head_kv * dim], v rows
  * [n_head_kv * vdim], f32.
- * store: per token t, q (and k) += bias; q, k <- RMS norm over the whole row * weight (when given); the first n_dims values of
- * every head of q and k are rotated as interleaved pairs by pos[t] * freqs[i]; q is written back in place, k and v (+ bias) go
- * to row cells[t] of the caches.  Strides in floats. */
+ * store: per token t, q (and k) += bias; q, k <- RMS norm * weight (when given) over the whole row, or with norm_per_head over
+ * every head by itself with one weight vector of dim values for all heads; the first n_dims values of every head of q and k are
+ * rotated by pos[t] * freqs[i] as interleaved pairs (2i, 2i + 1), or with rope_halves as pairs (i, i + n_dims / 2); q is written
+ * back in place, k and v (+ bias) go to row cells[t] of the caches.  Strides in floats. */
 typedef struct {
     float *q; int64_t q_stride;            /* [n_tokens][n_head * dim], rotated in place */
     const float *k; int64_t k_stride;      /* [n_tokens][n_head_kv * dim] */
@@ -228,12 +237,15 @@ typedef struct {
     float *v_cache; int64_t v_cache_stride;
     int32_t n_head, n_head_kv, dim, vdim, n_dims, n_tokens;
     float eps;
+    int32_t norm_per_head, rope_halves;
 } b200_qkv_store_args;
 B200_API int b200_op_qkv_store(const b200_qkv_store_args *a, b200_stream_t stream);
 
 /* score = scale * q . k; a token sees the cells of its own sequence with cell_pos <= tok_pos and (window == 0 or
- * tok_pos - cell_pos < window or cell_pos < keep_first); softmax in f32 whose denominator also holds exp(sink[h]) when sink !=
- * NULL (the sink has no key and no value).  dst [n_tokens][n_head * vdim].  bf16_products as for b200_op_latent_attn. */
+ * tok_pos - cell_pos < window or cell_pos < keep_first) and (chunk == 0 or tok_pos / chunk == cell_pos / chunk: positions are cut
+ * into chunks counted from 0 and nothing is seen across a cut); softmax in f32 whose denominator also holds exp(sink[h]) when
+ * sink != NULL (the sink has no key and no value).  gate != NULL: head h of token t is multiplied by sigmoid(gate[t * gate_stride
+ * + h]).  dst [n_tokens][n_head * vdim].  bf16_products as for b200_op_latent_attn. */
 typedef struct {
     const float *q; int64_t q_stride;
     const float *k_cache; int64_t k_cache_stride;
@@ -244,6 +256,8 @@ typedef struct {
     int32_t n_head, n_head_kv, dim, vdim, n_tokens, n_kv, window, keep_first;
     float scale;
     int32_t bf16_products;
+    int32_t chunk;
+    const float *gate; int64_t gate_stride;
 } b200_sink_attn_args;
 B200_API int b200_op_sink_attn(const b200_sink_attn_args *a, b200_stream_t stream);
 /* The same with a workspace of b200_sink_attn_workspace_bytes(a) bytes (16-byte aligned; 0: none needed): with few tokens and
@@ -270,6 +284,11 @@ B200_API int b200_op_linear_attn_scan(const b200_linear_attn_args *a, b200_strea
  * w[k] = s[ids[k]] / (sum_k s[ids[k]] + 1e-20) * scale.  n_expert <= 256, n_used <= 32.  ld_* in elements. */
 B200_API int b200_op_moe_route_grouped(const float *logits, int64_t ld_logits, const float *correction, int32_t *ids, int64_t ld_ids, float *w, int64_t ld_w,
                                        int32_t n_expert, int32_t n_used, int32_t n_group, int32_t n_group_used, float scale, int64_t n_tok, b200_stream_t stream);
+/* The same router with the score function as a parameter (enum b200_router_score: sigmoid per expert, or softmax over all
+ * experts) and, with keep_scores != 0, weights w[k] = s[ids[k]] * scale without the division by their sum. */
+B200_API int b200_op_moe_route_scored(const float *logits, int64_t ld_logits, const float *correction, int32_t *ids, int64_t ld_ids, float *w, int64_t ld_w,
+                                      int32_t n_expert, int32_t n_used, int32_t n_group, int32_t n_group_used, float scale, int32_t score, int32_t keep_scores,
+                                      int64_t n_tok, b200_stream_t stream);
 
 /* dst[t] = add0[t] + add1[t] + sum_k w[t][k] * y[t][k]; y [n, n_used, T] f32, w [n_used, T], add0 / add1 / dst [n, T] (add0, add1
  * optional); strides in floats. */

@@ -43,15 +43,20 @@ typedef struct {
     int32_t arch;
     int32_t n_seq_max;               /* sequences (and recurrent-state slots) that can be open at a time; 0 = 1 */
     float   logit_softcap;           /* > 0: logits = cap * tanh(logits / cap) (architectures with their own graph) */
+    float   embed_scale;             /* the embedding row is multiplied by this (0 reads as 1) */
+    float   residual_mult;           /* architectures that scale a sublayer's result before it joins the residual stream (0 reads as 1) */
 } b200_llama_params;
 
-enum b200_arch { B200_ARCH_LLAMA = 0, B200_ARCH_GENESUN = 1, B200_ARCH_GALIRAX = 2 };
+enum b200_arch { B200_ARCH_LLAMA = 0, B200_ARCH_GENESUN = 1, B200_ARCH_GALIRAX = 2, B200_ARCH_ZEVOPEL = 3 };
 enum b200_mixer {
     B200_MIXER_LATENT_ATTENTION = 1, B200_MIXER_MLSTM = 2,
     B200_MIXER_ATTENTION = 3, /* softmax attention of heads over kv_heads cached keys / values, per-head sink, optional window */
     B200_MIXER_LIGHTNING = 4, /* linear attention: a decayed outer-product state per head */
 };
-enum b200_mlp { B200_MLP_NONE = 0, B200_MLP_DENSE_POLYNORM = 1, B200_MLP_MOE_GATED = 2 /* routed gated experts */ };
+enum b200_mlp {
+    B200_MLP_NONE = 0, B200_MLP_DENSE_POLYNORM = 1, B200_MLP_MOE_GATED = 2 /* routed gated experts */,
+    B200_MLP_DENSE_GATED = 3, /* down(act(gate x) * up x), act by glu_kind */
+};
 enum b200_rope_scaling { B200_ROPE_SCALING_NONE = 0, B200_ROPE_SCALING_YARN = 1, B200_ROPE_SCALING_BANDS = 2 /* per wavelength band */ };
 
 /* One layer of an architecture with per-layer shapes (Genesun: config.json "layers"). */
@@ -83,6 +88,16 @@ typedef struct {
      * the sum of its two largest choice scores); weights s / sum(s over the chosen) * router_scale. */
     int32_t n_expert, n_expert_used, n_group, n_group_used;
     float   router_scale;
+    /* B200_MIXER_ATTENTION, further switches */
+    int32_t chunk;                   /* > 0: positions are cut into chunks of this many, counted from 0; a token sees its own chunk only */
+    int32_t qk_norm_per_head;        /* 1 (with qk_norm): the RMS norm runs over every head by itself, weights "q.norm" / "k.norm" of dim values */
+    int32_t rope_halves;             /* 1: entry i turns with entry i + rope_dims / 2 instead of the neighbours (2i, 2i + 1) */
+    int32_t head_gate;               /* 1: every head's result is multiplied by sigmoid(W_g x)_h, weights "g" [heads, width] */
+    /* feed-forward, further switches */
+    int32_t glu_kind;                /* enum b200_glu_kind (b200_ggml_ops.h) of the dense feed-forward or of the experts */
+    float   glu_limit, glu_alpha;    /* B200_GLU_SWISH_CLAMPED */
+    int32_t router_score;            /* enum b200_router_score */
+    int32_t router_keep_scores;      /* 1: an expert's weight is its score, not divided by the sum over the chosen */
 } b200_layer_params;
 
 

@@ -75,7 +75,8 @@ static bool ext_op_supported(const ggml_tensor *op) {
                    s[2]->ne[0] % op->op_params[3] == 0 && s[1]->ne[0] / op->op_params[2] == s[2]->ne[0] / op->op_params[3];
         case B200_EXT_SINK_ATTN:
             return f32_rows(s[0]) && f32_rows(s[1]) && f32_rows(s[2]) && (!s[3] || f32_vec(s[3])) && i32_vec(s[4]) && i32_vec(s[5]) && i32_vec(s[6]) && i32_vec(s[7]) &&
-                   f32_rows(op) && op->op_params[2] > 0 && op->op_params[2] <= 256 && op->op_params[7] > 0 && op->op_params[7] <= 256 && s[0]->ne[0] % op->op_params[2] == 0;
+                   f32_rows(op) && op->op_params[2] > 0 && op->op_params[2] <= 256 && op->op_params[7] > 0 && op->op_params[7] <= 256 && s[0]->ne[0] % op->op_params[2] == 0 &&
+                   (!s[8] || (f32_rows(s[8]) && s[8]->ne[0] == s[0]->ne[0] / op->op_params[2] && s[8]->ne[1] == s[0]->ne[1]));
         case B200_EXT_LINEAR_ATTN_SCAN:
             return f32_rows(s[0]) && f32_rows(s[1]) && f32_rows(s[2]) && f32_vec(s[3]) && i32_vec(s[4]) && f32_rows(s[5]) && f32_rows(op) && op->op_params[3] <= 256;
         case B200_EXT_MOE_ROUTE:
@@ -105,6 +106,8 @@ static void fill_sink_attn_args(const ggml_tensor *n, b200_sink_attn_args &a) {
     a.tok_seq = (const int32_t *)s[4]->data; a.tok_pos = (const int32_t *)s[5]->data;
     a.cell_seq = (const int32_t *)s[6]->data; a.cell_pos = (const int32_t *)s[7]->data; a.n_kv = (int32_t)s[6]->ne[0];
     a.dst = (float *)n->data; a.dst_stride = (int64_t)(n->nb[1] / 4);
+    a.chunk = n->op_params[8];
+    if (s[8]) { a.gate = (const float *)s[8]->data; a.gate_stride = (int64_t)(s[8]->nb[1] / 4); }
 }
 
 // the batched tensor-core form of an expert product over bf16 weights (the grouped GEMM of the quantised types)
@@ -197,7 +200,8 @@ static void run_ext(ExecCtx &x, const ggml_tensor *n) {
             const float *vec = s[3] ? (const float *)s[3]->data : nullptr;
             const int64_t nq = (int64_t)a.n_head * a.dim, nk = (int64_t)a.n_head_kv * a.dim, nv = (int64_t)a.n_head_kv * a.vdim;
             if (vec && n->op_params[6]) { a.q_bias = vec; a.k_bias = vec + nq; a.v_bias = vec + nq + nk; vec += nq + nk + nv; }
-            if (vec && n->op_params[7]) { a.q_norm = vec; a.k_norm = vec + nq; }
+            a.norm_per_head = n->op_params[7] == 2; a.rope_halves = n->op_params[8] != 0;
+            if (vec && n->op_params[7]) { a.q_norm = vec; a.k_norm = vec + (a.norm_per_head ? a.dim : nq); }
             a.pos = (const int32_t *)s[4]->data; a.freqs = (const float *)s[5]->data; a.cells = (const int32_t *)s[6]->data;
             a.k_cache = (float *)s[7]->data; a.k_cache_stride = (int64_t)(s[7]->nb[1] / 4);
             a.v_cache = (float *)s[8]->data; a.v_cache_stride = (int64_t)(s[8]->nb[1] / 4);
@@ -229,13 +233,13 @@ static void run_ext(ExecCtx &x, const ggml_tensor *n) {
         }
         case B200_EXT_MOE_ROUTE:
             // a row of the result: n_used weights, then the n_used expert ids as i32
-            B200_CHECK_RC(b200_op_moe_route_grouped((const float *)s[0]->data, (int64_t)(s[0]->nb[1] / 4), s[1] ? (const float *)s[1]->data : nullptr,
-                                                    (int32_t *)n->data + n->op_params[5], (int64_t)(n->nb[1] / 4), (float *)n->data, (int64_t)(n->nb[1] / 4), (int32_t)s[0]->ne[0],
-                                                    n->op_params[5], n->op_params[2], n->op_params[3], ext_f(n, 4), s[0]->ne[1], x.stream));
+            B200_CHECK_RC(b200_op_moe_route_scored((const float *)s[0]->data, (int64_t)(s[0]->nb[1] / 4), s[1] ? (const float *)s[1]->data : nullptr,
+                                                   (int32_t *)n->data + n->op_params[5], (int64_t)(n->nb[1] / 4), (float *)n->data, (int64_t)(n->nb[1] / 4), (int32_t)s[0]->ne[0],
+                                                   n->op_params[5], n->op_params[2], n->op_params[3], ext_f(n, 4), n->op_params[6], n->op_params[7], s[0]->ne[1], x.stream));
             break;
         case B200_EXT_SILU_MUL: {
             b200_tensor a = as_b200(s[0]), b = as_b200(s[1]), d = as_b200(n);
-            B200_CHECK_RC(b200_op_silu_mul_strided(&a, &b, &d, x.stream));
+            B200_CHECK_RC(b200_op_glu_strided(n->op_params[2], &a, &b, &d, ext_f(n, 3), ext_f(n, 4), x.stream));
             break;
         }
         case B200_EXT_MOE_COMBINE:

@@ -11,10 +11,12 @@ namespace b200 {
 using namespace opx;
 
 // ------------------------------------------------------------------------------------------------ bias + norm + rotation + cache store
-// One CTA per token.  The RMS statistics run over the whole projection (all heads at once); q is rewritten in place, k and v go
-// to the token's cache rows.
+// One CTA per token.  The RMS statistics run over the whole projection (all heads at once) or, with norm_per_head, over every
+// head by itself (a warp per head, the scales parked in shared memory); q is rewritten in place, k and v go to the token's cache
+// rows.  A rotated pair is (2i, 2i + 1) or, with rope_halves, (i, i + n_dims / 2).
 __global__ void __launch_bounds__(1024) qkv_store_kernel(const b200_qkv_store_args a) {
     __shared__ float sh[32];
+    extern __shared__ float head_scale[];  // norm_per_head: [n_head + n_head_kv]
     const int t = blockIdx.x;
     const int nq = a.n_head * a.dim, nk = a.n_head_kv * a.dim, nv = a.n_head_kv * a.vdim;
     float *q = a.q + (int64_t)t * a.q_stride;
@@ -22,36 +24,53 @@ __global__ void __launch_bounds__(1024) qkv_store_kernel(const b200_qkv_store_ar
     const int64_t cell = a.cells[t];
     float *kc = a.k_cache + cell * a.k_cache_stride, *vc = a.v_cache + cell * a.v_cache_stride;
     float qs = 1.f, ks = 1.f;
-    if (a.q_norm) {
-        float s = 0.f;
-        for (int i = threadIdx.x; i < nq; i += blockDim.x) { const float x = q[i] + (a.q_bias ? a.q_bias[i] : 0.f); s += x * x; }
-        qs = 1.0f / sqrtf(block_sum(s, sh) / (float)nq + a.eps);
-    }
-    if (a.k_norm) {
-        float s = 0.f;
-        for (int i = threadIdx.x; i < nk; i += blockDim.x) { const float x = k[i] + (a.k_bias ? a.k_bias[i] : 0.f); s += x * x; }
-        ks = 1.0f / sqrtf(block_sum(s, sh) / (float)nk + a.eps);
+    const bool per_head = a.norm_per_head != 0;
+    if (per_head) {
+        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
+        for (int hh = warp; hh < a.n_head + a.n_head_kv; hh += n_warps) {
+            const bool is_k = hh >= a.n_head;
+            if (!(is_k ? a.k_norm : a.q_norm)) continue;  // warp-uniform
+            const int e0 = (is_k ? hh - a.n_head : hh) * a.dim;
+            const float *src = is_k ? k : q, *bias = is_k ? a.k_bias : a.q_bias;
+            float s = 0.f;
+            for (int i = lane; i < a.dim; i += 32) { const float x = src[e0 + i] + (bias ? bias[e0 + i] : 0.f); s += x * x; }
+            s = warp_sum(s);
+            if (lane == 0) head_scale[hh] = 1.0f / sqrtf(s / (float)a.dim + a.eps);
+        }
+        __syncthreads();
+    } else {
+        if (a.q_norm) {
+            float s = 0.f;
+            for (int i = threadIdx.x; i < nq; i += blockDim.x) { const float x = q[i] + (a.q_bias ? a.q_bias[i] : 0.f); s += x * x; }
+            qs = 1.0f / sqrtf(block_sum(s, sh) / (float)nq + a.eps);
+        }
+        if (a.k_norm) {
+            float s = 0.f;
+            for (int i = threadIdx.x; i < nk; i += blockDim.x) { const float x = k[i] + (a.k_bias ? a.k_bias[i] : 0.f); s += x * x; }
+            ks = 1.0f / sqrtf(block_sum(s, sh) / (float)nk + a.eps);
+        }
     }
     const float p = (float)a.pos[t];
-    const int half = a.n_dims / 2, per_head = half + (a.dim - a.n_dims);  // work items of a head: rotated pairs, then single values
+    const int half = a.n_dims / 2, per_head_items = half + (a.dim - a.n_dims);  // work items of a head: rotated pairs, then single values
     for (int which = 0; which < 2; which++) {
         const float *src = which ? k : q;
         float *dst = which ? kc : q;
         const float *bias = which ? a.k_bias : a.q_bias, *nw = which ? a.k_norm : a.q_norm;
-        const float sc = which ? ks : qs;
         const int heads = which ? a.n_head_kv : a.n_head;
-        for (int idx = threadIdx.x; idx < heads * per_head; idx += blockDim.x) {
-            const int hh = idx / per_head, j = idx - hh * per_head;
+        for (int idx = threadIdx.x; idx < heads * per_head_items; idx += blockDim.x) {
+            const int hh = idx / per_head_items, j = idx - hh * per_head_items;
+            const float sc = (per_head && nw) ? head_scale[which * a.n_head + hh] : (which ? ks : qs);
+            const int wb = per_head ? hh * a.dim : 0;  // the weight of entry e is nw[e - wb]
             if (j >= half) {
                 const int e = hh * a.dim + a.n_dims + (j - half);
                 float x = src[e] + (bias ? bias[e] : 0.f);
-                if (nw) x = x * sc * nw[e];
+                if (nw) x = x * sc * nw[e - wb];
                 dst[e] = x;
                 continue;
             }
-            const int e0 = hh * a.dim + 2 * j, e1 = e0 + 1;
+            const int e0 = hh * a.dim + (a.rope_halves ? j : 2 * j), e1 = a.rope_halves ? e0 + half : e0 + 1;
             float u = src[e0] + (bias ? bias[e0] : 0.f), w = src[e1] + (bias ? bias[e1] : 0.f);
-            if (nw) { u = u * sc * nw[e0]; w = w * sc * nw[e1]; }
+            if (nw) { u = u * sc * nw[e0 - wb]; w = w * sc * nw[e1 - wb]; }
             float sn, cs;
             sincosf(p * a.freqs[j], &sn, &cs);
             dst[e0] = u * cs - w * sn;
@@ -61,8 +80,13 @@ __global__ void __launch_bounds__(1024) qkv_store_kernel(const b200_qkv_store_ar
     for (int i = threadIdx.x; i < nv; i += blockDim.x) vc[i] = v[i] + (a.v_bias ? a.v_bias[i] : 0.f);
 }
 
-__device__ __forceinline__ bool sa_visible(int cell_seq, int cell_pos, int seq, int pos, int window, int keep_first) {
-    return cell_seq == seq && cell_pos <= pos && (window <= 0 || pos - cell_pos < window || cell_pos < keep_first);
+// lo: the first position of the token's chunk (0 without chunks): nothing before it is seen
+__device__ __forceinline__ bool sa_visible(int cell_seq, int cell_pos, int seq, int pos, int window, int keep_first, int lo) {
+    return cell_seq == seq && cell_pos <= pos && cell_pos >= lo && (window <= 0 || pos - cell_pos < window || cell_pos < keep_first);
+}
+__device__ __forceinline__ int sa_chunk_start(int pos, int chunk) { return chunk > 0 ? pos - pos % chunk : 0; }
+__device__ __forceinline__ float sa_head_gate(const b200_sink_attn_args &a, int64_t t, int h) {
+    return a.gate ? 1.0f / (1.0f + expf(-a.gate[t * a.gate_stride + h])) : 1.0f;
 }
 
 // ------------------------------------------------------------------------------------------------ attention, f32 products
@@ -87,13 +111,13 @@ __global__ void __launch_bounds__(WARPS * 32) sink_attn_kernel(const b200_sink_a
     for (int i = 0; i < ND; i++) { const int j = lane + 32 * i; q[i] = j < D ? qp[j] * a.scale : 0.f; }
 #pragma unroll
     for (int i = 0; i < NV; i++) acc[i] = 0.f;
-    const int seq = a.tok_seq[t], pos = a.tok_pos[t];
+    const int seq = a.tok_seq[t], pos = a.tok_pos[t], lo = sa_chunk_start(pos, a.chunk);
     float m = -INFINITY, l = 0.f;
     const int per_split = ((a.n_kv + n_split - 1) / n_split + 31) & ~31;
     const int c_begin = (int)blockIdx.z * per_split, c_end = min(a.n_kv, c_begin + per_split);
     for (int cb = c_begin + warp * 32; cb < c_end; cb += WARPS * 32) {
         bool mine = false;
-        if (cb + lane < c_end) mine = sa_visible(a.cell_seq[cb + lane], a.cell_pos[cb + lane], seq, pos, a.window, a.keep_first);
+        if (cb + lane < c_end) mine = sa_visible(a.cell_seq[cb + lane], a.cell_pos[cb + lane], seq, pos, a.window, a.keep_first, lo);
         unsigned rest = __ballot_sync(0xffffffffu, mine);
         while (rest) {
             bool vis[SA_UNROLL];  // warp-uniform
@@ -159,7 +183,7 @@ __global__ void __launch_bounds__(WARPS * 32) sink_attn_kernel(const b200_sink_a
         }
         return;
     }
-    const float inv = L > 0.f ? 1.0f / L : 0.f;
+    const float inv = (L > 0.f ? 1.0f / L : 0.f) * sa_head_gate(a, t, h);
     float *out = a.dst + (int64_t)t * a.dst_stride + (int64_t)h * V;
     for (int j = threadIdx.x; j < V; j += blockDim.x) {
         float o = 0.f;
@@ -179,7 +203,7 @@ __global__ void __launch_bounds__(128) sink_attn_merge_kernel(const b200_sink_at
     for (int z = 0; z < n_split; z++) M = fmaxf(M, pp[(int64_t)z * (V + 2)]);
     float L = a.sink ? expf(sink - M) : 0.f;
     for (int z = 0; z < n_split; z++) { const float mz = pp[(int64_t)z * (V + 2)]; if (mz != -INFINITY) L += pp[(int64_t)z * (V + 2) + 1] * expf(mz - M); }
-    const float inv = L > 0.f ? 1.0f / L : 0.f;
+    const float inv = (L > 0.f ? 1.0f / L : 0.f) * sa_head_gate(a, t, h);
     float *out = a.dst + t * a.dst_stride + (int64_t)h * V;
     for (int j = threadIdx.x; j < V; j += blockDim.x) {
         float o = 0.f;
@@ -300,8 +324,9 @@ __global__ void __launch_bounds__(GM_WARPS * 32) sink_attn_mma_kernel(const b200
     const int wt = t0 + warp * 16;
     int my_seq = -2, my_pos = 0;
     if (lane < 16 && wt + lane < a.n_tokens) { my_seq = a.tok_seq[wt + lane]; my_pos = a.tok_pos[wt + lane]; }
-    const int rs0 = __shfl_sync(0xffffffffu, my_seq, g), rp0 = __shfl_sync(0xffffffffu, my_pos, g);
-    const int rs1 = __shfl_sync(0xffffffffu, my_seq, g + 8), rp1 = __shfl_sync(0xffffffffu, my_pos, g + 8);
+    const int my_lo = sa_chunk_start(my_pos, a.chunk);
+    const int rs0 = __shfl_sync(0xffffffffu, my_seq, g), rp0 = __shfl_sync(0xffffffffu, my_pos, g), rl0 = __shfl_sync(0xffffffffu, my_lo, g);
+    const int rs1 = __shfl_sync(0xffffffffu, my_seq, g + 8), rp1 = __shfl_sync(0xffffffffu, my_pos, g + 8), rl1 = __shfl_sync(0xffffffffu, my_lo, g + 8);
     __syncthreads();
 
     const int mi = lane >> 3, mr = lane & 7;
@@ -324,8 +349,8 @@ __global__ void __launch_bounds__(GM_WARPS * 32) sink_attn_mma_kernel(const b200
         bool see = false;
 #pragma unroll
         for (int i = 0; i < 16; i++) {
-            const int ts = __shfl_sync(0xffffffffu, my_seq, i), tp = __shfl_sync(0xffffffffu, my_pos, i);
-            see |= cs >= 0 && sa_visible(cs, cp, ts, tp, a.window, a.keep_first);
+            const int ts = __shfl_sync(0xffffffffu, my_seq, i), tp = __shfl_sync(0xffffffffu, my_pos, i), tl = __shfl_sync(0xffffffffu, my_lo, i);
+            see |= cs >= 0 && sa_visible(cs, cp, ts, tp, a.window, a.keep_first, tl);
         }
         const bool warp_sees = __any_sync(0xffffffffu, see);
         if (!__syncthreads_or(warp_sees)) continue;  // (also: the previous tile has been read by every warp)
@@ -356,8 +381,8 @@ __global__ void __launch_bounds__(GM_WARPS * 32) sink_attn_mma_kernel(const b200
             for (int e = 0; e < 2; e++) {
                 const int c = j * 8 + 2 * t4 + e;
                 const int xs = cseq[c], xp = cpos[c];
-                s[j][e] = sa_visible(xs, xp, rs0, rp0, a.window, a.keep_first) ? s[j][e] * a.scale : -INFINITY;
-                s[j][2 + e] = sa_visible(xs, xp, rs1, rp1, a.window, a.keep_first) ? s[j][2 + e] * a.scale : -INFINITY;
+                s[j][e] = sa_visible(xs, xp, rs0, rp0, a.window, a.keep_first, rl0) ? s[j][e] * a.scale : -INFINITY;
+                s[j][2 + e] = sa_visible(xs, xp, rs1, rp1, a.window, a.keep_first, rl1) ? s[j][2 + e] * a.scale : -INFINITY;
                 mx0 = fmaxf(mx0, s[j][e]); mx1 = fmaxf(mx1, s[j][2 + e]);
             }
         }
@@ -407,6 +432,7 @@ __global__ void __launch_bounds__(GM_WARPS * 32) sink_attn_mma_kernel(const b200
     for (int hh = 0; hh < 2; hh++) {
         const int t = wt + g + 8 * hh;
         if (t >= a.n_tokens) continue;
+        w[hh] *= sa_head_gate(a, t, h);
         float *out = a.dst + (int64_t)t * a.dst_stride + (int64_t)h * V;
 #pragma unroll
         for (int j = 0; j < 2 * VS; j++) {
@@ -564,7 +590,9 @@ extern "C" int b200_op_qkv_store(const b200_qkv_store_args *a, b200_stream_t str
     if (a->n_tokens == 0) return B200_OK;
     // few tokens (decode): a token's row is all the parallelism there is, so its CTA is wide
     const int threads = a->n_tokens <= 64 ? 1024 : 256;
-    qkv_store_kernel<<<(unsigned)a->n_tokens, threads, 0, (cudaStream_t)stream>>>(*a);
+    const size_t smem = a->norm_per_head ? (size_t)(a->n_head + a->n_head_kv) * sizeof(float) : 0;
+    OPX_REQUIRE(smem <= 32 * 1024, B200_ERR_UNSUPPORTED, "b200_op_qkv_store: per-head norms over at most 8192 heads");
+    qkv_store_kernel<<<(unsigned)a->n_tokens, threads, smem, (cudaStream_t)stream>>>(*a);
     B200_CUDA_TRY(cudaGetLastError());
     return B200_OK;
 }
@@ -581,7 +609,7 @@ extern "C" int b200_op_sink_attn(const b200_sink_attn_args *a, b200_stream_t str
 extern "C" int b200_op_sink_attn_ws(const b200_sink_attn_args *a, void *workspace, size_t workspace_bytes, b200_stream_t stream) {
     OPX_REQUIRE(a && a->q && a->k_cache && a->v_cache && a->cell_seq && a->cell_pos && a->tok_seq && a->tok_pos && a->dst, B200_ERR_INVALID, "b200_op_sink_attn: NULL argument");
     OPX_REQUIRE(a->n_head > 0 && a->n_head <= 65535 && a->n_head_kv > 0 && a->n_head % a->n_head_kv == 0 && a->dim > 0 && a->dim <= 256 && a->vdim > 0 && a->vdim <= 256 &&
-                a->n_tokens >= 0 && a->n_kv >= 0 && a->window >= 0 && a->keep_first >= 0, B200_ERR_UNSUPPORTED, "b200_op_sink_attn: head sizes up to 256, heads up to 65535");
+                a->n_tokens >= 0 && a->n_kv >= 0 && a->window >= 0 && a->keep_first >= 0 && a->chunk >= 0, B200_ERR_UNSUPPORTED, "b200_op_sink_attn: head sizes up to 256, heads up to 65535");
     if (a->n_tokens == 0) return B200_OK;
     const cudaStream_t st = (cudaStream_t)stream;
     if (sink_attn_mma_ok(a)) return launch_sink_attn_mma(a, st);

@@ -15,7 +15,7 @@
 // own (f32 weights, unrounded input, in every mode); bias, norm, rotation and the cache store are one launch; the experts of a
 // layer are two stacked tensors (gate over up per expert, and down) used through expert-indexed products; the weighted sum over
 // the chosen experts adds the mixer's result and the residual in the same launch.
-#include "host_model.h"
+#include "host_fused.h"
 
 namespace {
 
@@ -36,7 +36,6 @@ struct GxData {
 };
 GxData *gx(b200_llama *m) { return (GxData *)m->arch_data.get(); }
 
-struct Part { const char *leaf; int64_t rows; };
 int parts_proj1(const b200_layer_params &lp, Part out[8]) {
     int n = 0;
     const int64_t H = lp.heads, D = lp.dim, V = lp.vdim;
@@ -61,62 +60,6 @@ int parts_qkvec(const b200_layer_params &lp, Part out[8]) {
     if (lp.qk_norm) { out[n++] = {"mix.q.norm", nq}; out[n++] = {"mix.k.norm", nk}; }
     return n;
 }
-int64_t part_offset(const Part *p, int n, const char *leaf, int64_t *total, int64_t *rows = nullptr) {
-    int64_t off = 0, found = -1;
-    for (int i = 0; i < n; i++) {
-        if (!strcmp(p[i].leaf, leaf)) { found = off; if (rows) *rows = p[i].rows; }
-        off += p[i].rows;
-    }
-    if (total) *total = off;
-    return found;
-}
-
-// "l<i>.<leaf>" -> i, leaf
-bool split_name(const char *name, int *il, const char **leaf) {
-    if (name[0] != 'l' || name[1] < '0' || name[1] > '9') return false;
-    char *end = nullptr;
-    const long v = strtol(name + 1, &end, 10);
-    if (!end || *end != '.') return false;
-    *il = (int)v;
-    *leaf = end + 1;
-    return true;
-}
-// "mlp.e<j>.<which>" -> j, which
-bool split_expert(const char *leaf, int *e, const char **which) {
-    if (strncmp(leaf, "mlp.e", 5) != 0 || leaf[5] < '0' || leaf[5] > '9') return false;
-    char *end = nullptr;
-    const long v = strtol(leaf + 5, &end, 10);
-    if (!end || *end != '.') return false;
-    *e = (int)v;
-    *which = end + 1;
-    return true;
-}
-
-// `data` becomes bytes [off, off + bytes) of the tensor `fused` (created with the given shape at the first part)
-int place_into(b200_llama *m, const std::string &fused, const char *part_name, int type, int64_t ne0, int64_t ne1, int64_t ne2, size_t off, size_t bytes, const void *data) {
-    ggml_tensor *f = find_w(m, fused);
-    if (!f) {
-        m->weight_pool.emplace_back();
-        f = &m->weight_pool.back();
-        memset(f, 0, sizeof(*f));
-        set_shape(f, type, ne0, ne1, ne2, 1);
-        snprintf(f->name, sizeof(f->name), "%s", fused.c_str());
-        if (!alloc_in_buft(m, m->buft, f, GGML_BACKEND_BUFFER_USAGE_WEIGHTS)) {
-            m->weight_pool.pop_back();
-            b200::set_error("b200_llama_set_tensor: out of device memory for %s (%zu bytes)", fused.c_str(), nbytes(f));
-            return B200_ERR_NOMEM;
-        }
-        m->weights[fused] = f;
-        m->weight_bytes += (int64_t)nbytes(f);
-    }
-    LL_REQUIRE(f->type == type, B200_ERR_INVALID, "b200_llama_set_tensor: %s: the parts of %s must have one type", part_name, fused.c_str());
-    LL_REQUIRE(m->weights.find(part_name) == m->weights.end(), B200_ERR_INVALID, "b200_llama_set_tensor: duplicate tensor %s", part_name);
-    LL_REQUIRE(off + bytes <= nbytes(f), B200_ERR_INVALID, "b200_llama_set_tensor: %s does not fit %s", part_name, fused.c_str());
-    f->buffer->iface.set_tensor(f->buffer, f, data, off, bytes);
-    m->weights[part_name] = f;  // marks the part as present
-    return B200_OK;
-}
-
 int gx_place_tensor(b200_llama *m, const char *name, int type, int64_t ne0, int64_t ne1, int64_t ne2, const void *data) {
     int il = -1;
     const char *leaf = nullptr;
@@ -159,25 +102,6 @@ int gx_place_tensor(b200_llama *m, const char *name, int type, int64_t ne0, int6
         return place_into(m, pre + "mix.qkvec", name, type, total, 1, 1, (size_t)off * 4, (size_t)rows * 4, data);
     }
     return upload_tensor(m, name, type, ne0, ne1, ne2, data);
-}
-
-// per-pair rotation frequencies base^(-2i/dims), in double, rounded once; BANDS rescales by wavelength: short ones are kept, long
-// ones divided by the factor, the band between blended linearly in original / wavelength
-void rope_freqs(const b200_layer_params &lp, std::vector<float> &f) {
-    const int dims = lp.rope_dims;
-    f.resize((size_t)(dims / 2));
-    for (int i = 0; i < dims / 2; i++) {
-        double fi = pow((double)lp.rope_base, -2.0 * i / dims);
-        if (lp.rope_scaling == B200_ROPE_SCALING_BANDS) {
-            const double orig = lp.yarn_original, wl = 2.0 * M_PI / fi;
-            if (wl > orig / lp.band_low) fi /= lp.yarn_factor;
-            else if (!(wl < orig / lp.band_high)) {
-                const double s = (orig / wl - lp.band_low) / ((double)lp.band_high - lp.band_low);
-                fi = (1.0 - s) * fi / lp.yarn_factor + s * fi;
-            }
-        }
-        f[(size_t)i] = (float)fi;
-    }
 }
 
 int gx_finalize(b200_llama *m) {

@@ -262,6 +262,7 @@ struct Arch {
 const Arch *find_arch(int32_t id);
 const Arch *genesun_arch();
 const Arch *galirax_arch();
+const Arch *zevopel_arch();
 
 }  // namespace host
 }  // namespace b200

@@ -19,18 +19,38 @@ __device__ __forceinline__ void warp_argmax(float &v, int &i) {
 }
 
 constexpr int RG_WARPS = 4, RG_MAX_PER_LANE = 8;  // 256 experts
+// SCORE: enum b200_router_score.  The softmax runs over all experts of the token (maximum and sum across the warp); keep_scores
+// leaves the chosen experts' scores as they are instead of dividing them by their sum.
+template <int SCORE>
 __global__ void __launch_bounds__(RG_WARPS * 32) moe_route_grouped_kernel(const float *__restrict__ logits, int64_t ld_logits, const float *__restrict__ correction,
                                                                           int32_t *__restrict__ ids, int64_t ld_ids, float *__restrict__ w, int64_t ld_w, int n_expert,
-                                                                          int n_used, int n_group, int n_group_used, float scale, int64_t n_tok) {
+                                                                          int n_used, int n_group, int n_group_used, float scale, int keep_scores, int64_t n_tok) {
     const int64_t t = (int64_t)blockIdx.x * RG_WARPS + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
     if (t >= n_tok) return;
     float s[RG_MAX_PER_LANE], c[RG_MAX_PER_LANE];
+    if (SCORE == B200_ROUTER_SOFTMAX) {
+        float mx = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < RG_MAX_PER_LANE; i++) {
+            const int e = lane + 32 * i;
+            s[i] = e < n_expert ? logits[t * ld_logits + e] : -INFINITY;
+            mx = fmaxf(mx, s[i]);
+        }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+        float den = 0.f;
+#pragma unroll
+        for (int i = 0; i < RG_MAX_PER_LANE; i++) { s[i] = lane + 32 * i < n_expert ? expf(s[i] - mx) : 0.f; den += s[i]; }
+        den = warp_sum(den);
+#pragma unroll
+        for (int i = 0; i < RG_MAX_PER_LANE; i++) s[i] = s[i] / den;
+    }
 #pragma unroll
     for (int i = 0; i < RG_MAX_PER_LANE; i++) {
         const int e = lane + 32 * i;
         if (e < n_expert) {
-            s[i] = 1.0f / (1.0f + expf(-logits[t * ld_logits + e]));
+            if (SCORE == B200_ROUTER_SIGMOID) s[i] = 1.0f / (1.0f + expf(-logits[t * ld_logits + e]));
             c[i] = s[i] + (correction ? correction[e] : 0.f);
         } else {
             s[i] = 0.f; c[i] = -INFINITY;
@@ -93,7 +113,7 @@ __global__ void __launch_bounds__(RG_WARPS * 32) moe_route_grouped_kernel(const 
     }
     if (lane < n_used) {
         ids[t * ld_ids + lane] = mine_id;
-        w[t * ld_w + lane] = mine_w / (sum + 1e-20f) * scale;
+        w[t * ld_w + lane] = keep_scores ? mine_w * scale : mine_w / (sum + 1e-20f) * scale;
     }
 }
 
@@ -157,13 +177,24 @@ __global__ void __launch_bounds__(128) gemv_id_bf16_kernel(TD as, TD b, TD ids, 
     }
 }
 
-__global__ void silu_mul_strided_kernel(TD a, TD b, TD dst, int64_t n) {
+// enum b200_glu_kind
+template <int KIND>
+__device__ __forceinline__ float glu_value(float x, float u, float limit, float alpha) {
+    if (KIND == B200_GLU_GELU_TANH) return 0.5f * x * (1.0f + tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x))) * u;
+    if (KIND == B200_GLU_SWISH_CLAMPED) {
+        const float g = fminf(x, limit), c = fminf(fmaxf(u, -limit), limit);
+        return g / (1.0f + expf(-alpha * g)) * (c + 1.0f);
+    }
+    return x / (1.0f + expf(-x)) * u;
+}
+template <int KIND>
+__global__ void glu_strided_kernel(TD a, TD b, TD dst, int64_t n, float limit, float alpha) {
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     const int64_t i0 = i % dst.ne[0], i1 = (i / dst.ne[0]) % dst.ne[1], i2 = (i / (dst.ne[0] * dst.ne[1])) % dst.ne[2], i3 = i / (dst.ne[0] * dst.ne[1] * dst.ne[2]);
     const float x = *(const float *)(a.data + i0 * a.nb[0] + i1 * a.nb[1] + i2 * a.nb[2] + i3 * a.nb[3]);
     const float u = *(const float *)(b.data + i0 * b.nb[0] + i1 * b.nb[1] + i2 * b.nb[2] + i3 * b.nb[3]);
-    *(float *)(dst.data + i0 * dst.nb[0] + i1 * dst.nb[1] + i2 * dst.nb[2] + i3 * dst.nb[3]) = x / (1.0f + expf(-x)) * u;
+    *(float *)(dst.data + i0 * dst.nb[0] + i1 * dst.nb[1] + i2 * dst.nb[2] + i3 * dst.nb[3]) = glu_value<KIND>(x, u, limit, alpha);
 }
 
 __global__ void moe_combine_kernel(const float *__restrict__ y, int64_t y_s_slot, int64_t y_s_tok, const float *__restrict__ w, int64_t w_s_tok,
@@ -188,15 +219,26 @@ using namespace b200::opx;
 
 extern "C" int b200_op_moe_route_grouped(const float *logits, int64_t ld_logits, const float *correction, int32_t *ids, int64_t ld_ids, float *w, int64_t ld_w,
                                          int32_t n_expert, int32_t n_used, int32_t n_group, int32_t n_group_used, float scale, int64_t n_tok, b200_stream_t stream) {
+    return b200_op_moe_route_scored(logits, ld_logits, correction, ids, ld_ids, w, ld_w, n_expert, n_used, n_group, n_group_used, scale, B200_ROUTER_SIGMOID, 0, n_tok, stream);
+}
+
+extern "C" int b200_op_moe_route_scored(const float *logits, int64_t ld_logits, const float *correction, int32_t *ids, int64_t ld_ids, float *w, int64_t ld_w,
+                                        int32_t n_expert, int32_t n_used, int32_t n_group, int32_t n_group_used, float scale, int32_t score, int32_t keep_scores,
+                                        int64_t n_tok, b200_stream_t stream) {
     OPX_REQUIRE(logits && ids && w, B200_ERR_INVALID, "b200_op_moe_route_grouped: NULL argument");
+    OPX_REQUIRE(score == B200_ROUTER_SIGMOID || score == B200_ROUTER_SOFTMAX, B200_ERR_INVALID, "b200_op_moe_route_scored: unknown score function %d", score);
     OPX_REQUIRE(n_expert > 0 && n_expert <= 32 * RG_MAX_PER_LANE && n_used > 0 && n_used <= 32 && n_used <= n_expert && n_tok >= 0, B200_ERR_UNSUPPORTED,
                 "b200_op_moe_route_grouped: at most 256 experts, 32 per token");
     if (n_group < 1) n_group = 1;
     OPX_REQUIRE(n_group <= 32 && n_expert % n_group == 0 && n_group_used >= 1 && n_group_used <= n_group && (int64_t)n_group_used * (n_expert / n_group) >= n_used, B200_ERR_INVALID,
                 "b200_op_moe_route_grouped: %d groups (%d kept) do not fit %d experts, %d per token", n_group, n_group_used, n_expert, n_used);
     if (n_tok == 0) return B200_OK;
-    moe_route_grouped_kernel<<<grid1d(n_tok, RG_WARPS), RG_WARPS * 32, 0, (cudaStream_t)stream>>>(logits, ld_logits, correction, ids, ld_ids, w, ld_w, n_expert, n_used, n_group,
-                                                                                                   n_group_used, scale, n_tok);
+    if (score == B200_ROUTER_SOFTMAX)
+        moe_route_grouped_kernel<B200_ROUTER_SOFTMAX><<<grid1d(n_tok, RG_WARPS), RG_WARPS * 32, 0, (cudaStream_t)stream>>>(logits, ld_logits, correction, ids, ld_ids, w, ld_w, n_expert,
+                                                                                                                          n_used, n_group, n_group_used, scale, keep_scores, n_tok);
+    else
+        moe_route_grouped_kernel<B200_ROUTER_SIGMOID><<<grid1d(n_tok, RG_WARPS), RG_WARPS * 32, 0, (cudaStream_t)stream>>>(logits, ld_logits, correction, ids, ld_ids, w, ld_w, n_expert,
+                                                                                                                          n_used, n_group, n_group_used, scale, keep_scores, n_tok);
     B200_CUDA_TRY(cudaGetLastError());
     return B200_OK;
 }
@@ -225,12 +267,20 @@ extern "C" int b200_op_mul_mat_id_float(const b200_tensor *as, const b200_tensor
 }
 
 extern "C" int b200_op_silu_mul_strided(const b200_tensor *a, const b200_tensor *b, const b200_tensor *dst, b200_stream_t stream) {
-    OPX_REQUIRE(a && b && dst && a->data && b->data && dst->data, B200_ERR_INVALID, "b200_op_silu_mul_strided: NULL argument");
+    return b200_op_glu_strided(B200_GLU_SILU, a, b, dst, 0.0f, 0.0f, stream);
+}
+
+extern "C" int b200_op_glu_strided(int kind, const b200_tensor *a, const b200_tensor *b, const b200_tensor *dst, float limit, float alpha, b200_stream_t stream) {
+    OPX_REQUIRE(a && b && dst && a->data && b->data && dst->data, B200_ERR_INVALID, "b200_op_glu_strided: NULL argument");
     OPX_REQUIRE(a->type == B200_TYPE_F32 && b->type == B200_TYPE_F32 && dst->type == B200_TYPE_F32 && same_shape(a, dst) && same_shape(b, dst), B200_ERR_UNSUPPORTED,
-                "b200_op_silu_mul_strided: f32 tensors of one shape only");
+                "b200_op_glu_strided: f32 tensors of one shape only");
+    OPX_REQUIRE(kind == B200_GLU_SILU || kind == B200_GLU_GELU_TANH || kind == B200_GLU_SWISH_CLAMPED, B200_ERR_INVALID, "b200_op_glu_strided: unknown kind %d", kind);
     const int64_t n = nelements(dst);
     if (n == 0) return B200_OK;
-    silu_mul_strided_kernel<<<grid1d(n, 256), 256, 0, (cudaStream_t)stream>>>(td(a), td(b), td(dst), n);
+    const cudaStream_t st = (cudaStream_t)stream;
+    if (kind == B200_GLU_GELU_TANH) glu_strided_kernel<B200_GLU_GELU_TANH><<<grid1d(n, 256), 256, 0, st>>>(td(a), td(b), td(dst), n, limit, alpha);
+    else if (kind == B200_GLU_SWISH_CLAMPED) glu_strided_kernel<B200_GLU_SWISH_CLAMPED><<<grid1d(n, 256), 256, 0, st>>>(td(a), td(b), td(dst), n, limit, alpha);
+    else glu_strided_kernel<B200_GLU_SILU><<<grid1d(n, 256), 256, 0, st>>>(td(a), td(b), td(dst), n, limit, alpha);
     B200_CUDA_TRY(cudaGetLastError());
     return B200_OK;
 }

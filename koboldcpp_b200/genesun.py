@@ -93,7 +93,7 @@ class SequenceModel:
     """A model of an architecture with sequences, resident on one device: tensors in, batch steps out."""
 
     def __init__(self, arch: int, width: int, vocab: int, layers: list[LayerParams], eps: float, n_ctx: int, n_seq_max: int, max_batch: int, device: int = 0,
-                 logit_softcap: float = 0.0, order: list[int] | None = None):
+                 logit_softcap: float = 0.0, order: list[int] | None = None, embed_scale: float = 1.0, residual_mult: float = 1.0):
         """order: the layer of every run, in execution order (None: every layer once); a layer that runs several times has a cache
         or state per run."""
         L = _l()
@@ -103,7 +103,7 @@ class SequenceModel:
         self.n_ctx = (max(n_ctx, 1) + 255) // 256 * 256
         self.n_seq_max, self.max_batch = n_seq_max, max_batch
         p = LlamaParams(n_embd=width, n_layer=len(layers), n_vocab=vocab, n_ctx=self.n_ctx, rms_eps=eps, main_device=device, arch=arch, n_seq_max=n_seq_max,
-                        logit_softcap=logit_softcap)
+                        logit_softcap=logit_softcap, embed_scale=embed_scale, residual_mult=residual_mult)
         h = C.c_void_p()
         check(L.b200_llama_new(C.byref(p), C.byref(h)), "b200_llama_new")
         self.h = h

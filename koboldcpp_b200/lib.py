@@ -87,7 +87,7 @@ class QkvStoreArgs(C.Structure):
                 ("q_bias", C.c_void_p), ("k_bias", C.c_void_p), ("v_bias", C.c_void_p), ("q_norm", C.c_void_p), ("k_norm", C.c_void_p),
                 ("pos", C.c_void_p), ("cells", C.c_void_p), ("freqs", C.c_void_p), ("k_cache", C.c_void_p), ("k_cache_stride", C.c_int64),
                 ("v_cache", C.c_void_p), ("v_cache_stride", C.c_int64), ("n_head", C.c_int32), ("n_head_kv", C.c_int32), ("dim", C.c_int32),
-                ("vdim", C.c_int32), ("n_dims", C.c_int32), ("n_tokens", C.c_int32), ("eps", C.c_float)]
+                ("vdim", C.c_int32), ("n_dims", C.c_int32), ("n_tokens", C.c_int32), ("eps", C.c_float), ("norm_per_head", C.c_int32), ("rope_halves", C.c_int32)]
 
 
 class SinkAttnArgs(C.Structure):
@@ -96,7 +96,7 @@ class SinkAttnArgs(C.Structure):
                 ("v_cache_stride", C.c_int64), ("cell_seq", C.c_void_p), ("cell_pos", C.c_void_p), ("tok_seq", C.c_void_p), ("tok_pos", C.c_void_p),
                 ("sink", C.c_void_p), ("dst", C.c_void_p), ("dst_stride", C.c_int64), ("n_head", C.c_int32), ("n_head_kv", C.c_int32), ("dim", C.c_int32),
                 ("vdim", C.c_int32), ("n_tokens", C.c_int32), ("n_kv", C.c_int32), ("window", C.c_int32), ("keep_first", C.c_int32), ("scale", C.c_float),
-                ("bf16_products", C.c_int32)]
+                ("bf16_products", C.c_int32), ("chunk", C.c_int32), ("gate", C.c_void_p), ("gate_stride", C.c_int64)]
 
 
 class LinearAttnArgs(C.Structure):
@@ -186,6 +186,9 @@ _OPS_SIGS = {
     "b200_op_linear_attn_scan": (C.c_int, [C.POINTER(LinearAttnArgs), C.c_void_p]),
     "b200_op_moe_route_grouped": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
                                             C.c_float, C.c_int64, C.c_void_p]),
+    "b200_op_moe_route_scored": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
+                                           C.c_float, C.c_int32, C.c_int32, C.c_int64, C.c_void_p]),
+    "b200_op_glu_strided": (C.c_int, [C.c_int, C.POINTER(Tensor), C.POINTER(Tensor), C.POINTER(Tensor), C.c_float, C.c_float, C.c_void_p]),
     "b200_op_moe_combine": (C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64,
                                       C.c_int64, C.c_int32, C.c_int64, C.c_void_p]),
     "b200_op_mul_mat_id_float": (C.c_int, [C.POINTER(Tensor), C.POINTER(Tensor), C.POINTER(Tensor), C.POINTER(Tensor), C.c_void_p]),

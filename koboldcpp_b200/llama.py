@@ -19,7 +19,8 @@ class LlamaParams(C.Structure):
                 ("type_k", C.c_int32), ("type_v", C.c_int32), ("rope_neox", C.c_int32), ("n_ctx_orig", C.c_int32),
                 ("rms_eps", C.c_float), ("rope_freq_base", C.c_float), ("rope_freq_scale", C.c_float),
                 ("main_device", C.c_int32), ("n_split_devices", C.c_int32), ("tensor_split", C.c_float * 16),
-                ("tp_rank", C.c_int32), ("tp_world", C.c_int32), ("arch", C.c_int32), ("n_seq_max", C.c_int32), ("logit_softcap", C.c_float)]
+                ("tp_rank", C.c_int32), ("tp_world", C.c_int32), ("arch", C.c_int32), ("n_seq_max", C.c_int32), ("logit_softcap", C.c_float),
+                ("embed_scale", C.c_float), ("residual_mult", C.c_float)]
 
 
 class LayerParams(C.Structure):
@@ -30,7 +31,9 @@ class LayerParams(C.Structure):
                 ("mlp", C.c_int32), ("ff", C.c_int32),
                 ("kv_heads", C.c_int32), ("keep_first", C.c_int32), ("qkv_bias", C.c_int32), ("qk_norm", C.c_int32), ("rope_scaling", C.c_int32),
                 ("band_low", C.c_float), ("band_high", C.c_float),
-                ("n_expert", C.c_int32), ("n_expert_used", C.c_int32), ("n_group", C.c_int32), ("n_group_used", C.c_int32), ("router_scale", C.c_float)]
+                ("n_expert", C.c_int32), ("n_expert_used", C.c_int32), ("n_group", C.c_int32), ("n_group_used", C.c_int32), ("router_scale", C.c_float),
+                ("chunk", C.c_int32), ("qk_norm_per_head", C.c_int32), ("rope_halves", C.c_int32), ("head_gate", C.c_int32),
+                ("glu_kind", C.c_int32), ("glu_limit", C.c_float), ("glu_alpha", C.c_float), ("router_score", C.c_int32), ("router_keep_scores", C.c_int32)]
 
 
 _SIGS = {

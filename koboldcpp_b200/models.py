@@ -4,12 +4,13 @@ from __future__ import annotations
 import json
 from pathlib import Path
 
-from . import galirax, genesun
+from . import galirax, genesun, zevopel
 from .lib import B200Error
 
 ARCHITECTURES = {
     "Genesun": genesun.load,
     "Galirax": galirax.load,
+    "Zevopel": zevopel.load,
 }
 
 
