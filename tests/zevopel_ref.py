@@ -176,40 +176,69 @@ def forward(tokens, W, cfg, pos0=0, streams=None):
 
 
 # ------------------------------------------------------------------------------------------------ random models for tests
-def random_weights(cfg, rng, sd=None):
-    """name -> float64 array whose values are exactly representable in bfloat16."""
+def dense(ff=48):
+    return {"kind": "dense", "ff": ff}
+
+
+def moe(ff=24, experts=6, top=2, limit=1.25):
+    return {"kind": "moe", "expert": {"ff": ff, "limit": limit}, "router": {"experts": experts, "top": top}}
+
+
+def attn_layer(heads=4, kv_heads=2, dim=16, vdim=24, rot_dims=8, base=1000.0, scaling=True, chunk=0, scale=None, mlp="dense"):
+    rot = {"base": base, "dims": rot_dims}
+    if scaling:
+        rot["scaling"] = {"factor": 4.0, "low": 1.0, "high": 3.0, "original": 48}
+    mx = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "rot": rot, "scale": scale if scale is not None else 1.3 / math.sqrt(dim)}
+    if chunk:
+        mx["mask"] = {"size": chunk}
+    return {"type": "attention", "mixer": mx, "mlp": dense() if mlp == "dense" else moe() if mlp == "moe" else mlp}
+
+
+def make_config(layers, width=40, vocab=61, eps=1e-5, embed_scale=2.0, residual_mult=0.8):
+    return {"architecture": "Zevopel", "width": width, "vocab": vocab, "norm": {"eps": eps}, "embedding": {"scale": embed_scale}, "residual_mult": residual_mult, "layers": layers}
+
+
+def random_weights(cfg, seed=0, gain=1.0):
+    """name -> float64 arrays whose values bfloat16 holds exactly, so that the served (bf16) and the exact (f32) modes read the same
+    model.  The experts' products are large enough for both clamps to act."""
+    rng = np.random.default_rng(seed)
     Wd, Vc = cfg["width"], cfg["vocab"]
     W = {}
 
-    def mat(name, o, i, s):
-        W[name] = bf16_round(rng.standard_normal((o, i)) * s).astype(np.float64)
+    def mat(name, rows, cols, g=1.0):
+        W[name] = bf16_round(rng.standard_normal((rows, cols)) * g * gain / math.sqrt(cols)).astype(np.float64)
 
-    def vec(name, n, s, mean=0.0):
-        W[name] = bf16_round(mean + rng.standard_normal(n) * s).astype(np.float64)
+    def vec(name, n, mean=0.0, spread=0.3):
+        W[name] = bf16_round(mean + spread * rng.standard_normal(n)).astype(np.float64)
 
-    mat("embed", Vc, Wd, 1.0)
-    mat("head", Vc, Wd, Wd ** -0.5)
-    vec("final.norm", Wd, 0.2)
+    W["embed"] = bf16_round(rng.standard_normal((Vc, Wd))).astype(np.float64)
+    mat("head", Vc, Wd, 3.0)
+    vec("final.norm", Wd, 0.0, 0.2)
     for il, L in enumerate(cfg["layers"]):
-        p = f"l{il}."
-        mx = L["mixer"]
+        p, mx = f"l{il}.", L["mixer"]
         H, G, D, V = mx["heads"], mx["kv_heads"], mx["dim"], mx["vdim"]
-        mat(p + "mix.q", H * D, Wd, Wd ** -0.5); mat(p + "mix.k", G * D, Wd, Wd ** -0.5); mat(p + "mix.v", G * V, Wd, Wd ** -0.5)
-        mat(p + "mix.g", H, Wd, Wd ** -0.5); mat(p + "mix.o", Wd, H * V, (H * V) ** -0.5)
-        vec(p + "mix.q.norm", D, 0.2, 1.0); vec(p + "mix.k.norm", D, 0.2, 1.0); vec(p + "mix.sink", H, 1.0)
-        for n in ("norm1", "norm2"):
-            vec(p + n, Wd, 0.2)
-        for n in ("ls1", "ls2"):
-            vec(p + n, Wd, 0.2, 1.0)
+        mat(p + "mix.q", H * D, Wd); mat(p + "mix.k", G * D, Wd); mat(p + "mix.v", G * V, Wd); mat(p + "mix.g", H, Wd, 1.5); mat(p + "mix.o", Wd, H * V)
+        vec(p + "mix.q.norm", D, 1.0, 0.3); vec(p + "mix.k.norm", D, 1.0, 0.3); vec(p + "mix.sink", H, 0.5, 1.0)
+        vec(p + "norm1", Wd, 0.0, 0.2); vec(p + "ls1", Wd, 1.0, 0.3)
         mlp = L.get("mlp")
         if mlp is None:
             continue
+        vec(p + "norm2", Wd, 0.0, 0.2); vec(p + "ls2", Wd, 1.0, 0.3)
         if mlp["kind"] == "dense":
             F = mlp["ff"]
-            mat(p + "mlp.gate", F, Wd, Wd ** -0.5); mat(p + "mlp.up", F, Wd, Wd ** -0.5); mat(p + "mlp.down", Wd, F, F ** -0.5)
+            mat(p + "mlp.gate", F, Wd); mat(p + "mlp.up", F, Wd); mat(p + "mlp.down", Wd, F)
         else:
-            F = mlp["expert"]["ff"]
-            mat(p + "mlp.router", mlp["router"]["experts"], Wd, 2.0 * Wd ** -0.5)
-            for e in range(mlp["router"]["experts"]):
-                mat(p + f"mlp.e{e}.gate", F, Wd, 2.0 * Wd ** -0.5); mat(p + f"mlp.e{e}.up", F, Wd, 2.0 * Wd ** -0.5); mat(p + f"mlp.e{e}.down", Wd, F, F ** -0.5)
+            F, E = mlp["expert"]["ff"], mlp["router"]["experts"]
+            mat(p + "mlp.router", E, Wd, 1.5)
+            for e in range(E):
+                mat(p + f"mlp.e{e}.gate", F, Wd, 0.7); mat(p + f"mlp.e{e}.up", F, Wd, 0.7); mat(p + f"mlp.e{e}.down", Wd, F)
     return W
+
+
+def as_tensors(W):
+    """name -> (dtype, shape, raw bytes), the form the loader takes: matrices and vectors as bf16 bits."""
+    out = {}
+    for name, a in W.items():
+        bits = (np.ascontiguousarray(a, dtype=np.float32).view(np.uint32) >> 16).astype(np.uint16)
+        out[name] = ("BF16", tuple(a.shape), bits.view(np.uint8).reshape(-1))
+    return out
