@@ -741,6 +741,90 @@ def galirax_step_cost(cfg: dict, n_tokens: int, n_seq: int, ctx: int) -> dict:
     return {"weight_bytes": 2 * wparams, "cache_bytes": cache, "state_bytes": state, "flop": 2 * active * n_tokens + attn_flop}
 
 
+# ------------------------------------------------------------------------------------------------ --design zevopel
+# The same measurement for the Zevopel design (norms behind the sublayers, chunked grouped-query attention with per-head q / k norms,
+# sinks and head gates, a gated gelu feed-forward in the odd layers and softmax-routed clamped experts in the even ones), beside the
+# closest existing model of the framework: Galirax with plain attention layers and routed experts at equal width, depth, heads and
+# expert size, through the same loader, cache and engine.
+ZEVOPEL_CHUNK = 8192
+
+
+def zevopel_config(size: str) -> dict:
+    import math
+    W, (h, g, d, v), (ne, top, ff, _ng, _nk), _window = GALIRAX_SIZES[size]
+    rot = {"base": 500000.0, "dims": d // 2, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}
+    mixer = {"heads": h, "kv_heads": g, "dim": d, "vdim": v, "rot": rot, "scale": 1.0 / math.sqrt(d), "mask": {"size": ZEVOPEL_CHUNK}}
+    moe = {"kind": "moe", "expert": {"ff": ff, "limit": 7.0}, "router": {"experts": ne, "top": top}}
+    dense = {"kind": "dense", "ff": top * ff}  # as many active parameters as the routed layers
+    layers = [{"type": "attention", "mixer": mixer, "mlp": moe if il % 2 == 0 else dense} for il in range(DESIGN_LAYERS)]
+    return {"architecture": "Zevopel", "width": W, "vocab": DESIGN_VOCAB, "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0}, "residual_mult": 1.0, "layers": layers}
+
+
+def zevopel_tensor_shapes(cfg: dict) -> dict:
+    W, V = cfg["width"], cfg["vocab"]
+    t = {"embed": (V, W), "head": (V, W), "final.norm": (W,)}
+    for i, L in enumerate(cfg["layers"]):
+        p, mx = f"l{i}.", L["mixer"]
+        H, G, D, Vd = mx["heads"], mx["kv_heads"], mx["dim"], mx["vdim"]
+        t.update({p + "norm1": (W,), p + "norm2": (W,), p + "ls1": (W,), p + "ls2": (W,), p + "mix.q": (H * D, W), p + "mix.k": (G * D, W), p + "mix.v": (G * Vd, W),
+                  p + "mix.g": (H, W), p + "mix.o": (W, H * Vd), p + "mix.q.norm": (D,), p + "mix.k.norm": (D,), p + "mix.sink": (H,)})
+        if L["mlp"]["kind"] == "dense":
+            F = L["mlp"]["ff"]
+            t.update({p + "mlp.gate": (F, W), p + "mlp.up": (F, W), p + "mlp.down": (W, F)})
+        else:
+            E, F = L["mlp"]["router"]["experts"], L["mlp"]["expert"]["ff"]
+            t[p + "mlp.router"] = (E, W)
+            for e in range(E):
+                t.update({f"{p}mlp.e{e}.gate": (F, W), f"{p}mlp.e{e}.up": (F, W), f"{p}mlp.e{e}.down": (W, F)})
+    return t
+
+
+def zevopel_random_tensors(cfg: dict):
+    out = random_tensors(zevopel_tensor_shapes(cfg))
+    for name, (dt, shape, raw) in list(out.items()):
+        leaf = name.split(".")[-1]
+        if leaf in ("ls1", "ls2"):  # the per-channel scales sit near one, the norm weights (stored as the distance from one) near zero
+            out[name] = (dt, shape, np.full(int(np.prod(shape)), 1.0, np.float32).view(np.uint8))
+        elif leaf in ("norm1", "norm2") or name == "final.norm":
+            out[name] = (dt, shape, np.zeros(int(np.prod(shape)), np.float32).view(np.uint8))
+    return out
+
+
+def zevopel_step_cost(cfg: dict, n_tokens: int, n_seq: int, ctx: int) -> dict:
+    """Algorithmic bytes (bf16 weights once -- of the experts those a batch of this size can reach --, the visible f32 cache rows of the
+    batch) and FLOPs of one step."""
+    W, V = cfg["width"], cfg["vocab"]
+    wparams = active = W * V  # head
+    cache = attn_flop = 0
+    for L in cfg["layers"]:
+        mx = L["mixer"]
+        H, G, D, Vd = mx["heads"], mx["kv_heads"], mx["dim"], mx["vdim"]
+        p = W * (H * D + G * D + G * Vd + H) + W * H * Vd
+        vis = min(ctx, (mx.get("mask") or {}).get("size", 0) or ctx)
+        cache += n_seq * vis * G * (D + Vd) * 4
+        attn_flop += 2 * n_tokens * H * (vis if n_tokens == n_seq else ctx // 2) * (D + Vd)
+        wparams += p
+        active += p
+        if L["mlp"]["kind"] == "dense":
+            wparams += 3 * W * L["mlp"]["ff"]
+            active += 3 * W * L["mlp"]["ff"]
+        else:
+            r, F = L["mlp"]["router"], L["mlp"]["expert"]["ff"]
+            wparams += W * r["experts"] + 3 * W * F * min(r["experts"], n_tokens * r["top"])
+            active += W * r["experts"] + 3 * W * F * r["top"]
+    return {"weight_bytes": 2 * wparams, "cache_bytes": cache, "state_bytes": 0, "flop": 2 * active * n_tokens + attn_flop}
+
+
+def zevopel_beside_config(size: str) -> dict:
+    """Galirax at equal width, depth, heads and expert size: plain attention layers (sink, no window), routed experts in every layer."""
+    import math
+    W, (h, g, d, v), (ne, top, ff, ng, nk), _window = GALIRAX_SIZES[size]
+    mlp = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": ne, "top": top, "groups": {"count": ng, "keep": nk}, "scale": 2.0}}
+    rot = {"base": 500000.0, "dims": d // 2, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}
+    layers = [{"type": "attention", "mixer": {"heads": h, "kv_heads": g, "dim": d, "vdim": v, "rot": rot, "scale": 1.0 / math.sqrt(d)}, "mlp": mlp} for _ in range(DESIGN_LAYERS)]
+    return {"architecture": "Galirax", "width": W, "vocab": DESIGN_VOCAB, "norm": {"eps": 1e-5}, "logit_softcap": 30.0, "layers": layers}
+
+
 def galirax_llama_shape(size: str):
     import koboldcpp_b200.llama as LL
     W, (h, g, d, v), (ne, top, ff, ng, nk), window = GALIRAX_SIZES[size]
@@ -778,8 +862,12 @@ def random_tensors(shapes: dict, seed: int = 1):
 
 
 def design_table():
-    from koboldcpp_b200 import galirax, genesun
+    from koboldcpp_b200 import galirax, genesun, zevopel
     return {
+        "zevopel": {"sizes": GALIRAX_SIZES, "config": zevopel_config, "tensors": zevopel_random_tensors, "cost": zevopel_step_cost, "build": zevopel.build,
+                    "beside_design": {"name": "galirax", "config": zevopel_beside_config, "tensors": lambda cfg: random_tensors(galirax_tensor_shapes(cfg)),
+                                      "cost": galirax_step_cost, "build": galirax.build},
+                    "beside": "Galirax (attention with sinks + routed experts in every layer), equal width / depth / heads / expert size, bf16"},
         "genesun": {"sizes": DESIGN_SIZES, "config": genesun_config, "tensors": lambda cfg: genesun_random_tensors(cfg), "cost": genesun_step_cost, "build": genesun.build,
                     "llama": genesun_llama_shape, "beside": "llama Q4_K_M, equal width / depth / ff"},
         "galirax": {"sizes": GALIRAX_SIZES, "config": galirax_config, "tensors": lambda cfg: random_tensors(galirax_tensor_shapes(cfg)), "cost": galirax_step_cost,
@@ -822,16 +910,10 @@ def design_leg(args) -> int:
         return total / steps
 
     steps, warmup = max(3, min(args.steps, 20)), max(3, args.warmup)
-    rows = []
-    sizes = [s for s in DS["sizes"] if not args.design_sizes or s in args.design_sizes.split(",")]
-    for size in sizes:
-        cfg = DS["config"](size)
-        W = cfg["width"]
-        row = {"size": size, "width": W, "layers": DESIGN_LAYERS, "ctx": DESIGN_CTX}
+
+    def measure_design(DS, name, cfg, row, prompt, rng):
         m = DS["build"](cfg, DS["tensors"](cfg), dtype="bfloat16", n_ctx=8 * DESIGN_CTX + 256, n_seq_max=8, max_batch=DESIGN_PP)
         eng = Engine(m)
-        rng = np.random.default_rng(0)
-        prompt = rng.integers(0, DESIGN_VOCAB, DESIGN_PP).tolist()
         # prefill: one prompt of DESIGN_PP tokens
         t0 = time.time()
         eng.step([("p", prompt, [DESIGN_PP - 1])])
@@ -860,6 +942,22 @@ def design_leg(args) -> int:
             for rid in ids:
                 eng.finish(rid)
         m.close()
+
+    rows = []
+    sizes = [s for s in DS["sizes"] if not args.design_sizes or s in args.design_sizes.split(",")]
+    for size in sizes:
+        cfg = DS["config"](size)
+        W = cfg["width"]
+        row = {"size": size, "width": W, "layers": DESIGN_LAYERS, "ctx": DESIGN_CTX}
+        rng = np.random.default_rng(0)
+        prompt = rng.integers(0, DESIGN_VOCAB, DESIGN_PP).tolist()
+        measure_design(DS, name, cfg, row, prompt, rng)
+        if "beside_design" in DS:  # the closest existing design at equal size, through the same loader, cache and engine
+            BD = DS["beside_design"]
+            measure_design(BD, BD["name"], BD["config"](size), row, prompt, rng)
+            rows.append(row)
+            print(json.dumps({"design_size": row}), file=sys.stderr, flush=True)
+            continue
         # the llama decoder at equal width, depth and feed-forward size
         shape = DS["llama"](size)
         lm = LL.LlamaModel(shape, DESIGN_CTX + 256, F16)
@@ -897,9 +995,9 @@ def main() -> int:
     ap.add_argument("--cpu-budget", type=float, default=18.0)
     ap.add_argument("--no-tp70", action="store_true", default=bool(os.environ.get("B200_BENCH_NO_TP70")),
                     help="skip the auxiliary 70B tensor-parallel leg (BASELINE.json configs[4])")
-    ap.add_argument("--design", default="", choices=["", "genesun", "galirax"],
-                    help="instead of the default workload: prefill / decode of this design at real layer shapes beside the llama decoder at equal size")
-    ap.add_argument("--design-sizes", default="", help="comma-separated subset of " + ",".join(DESIGN_SIZES))
+    ap.add_argument("--design", default="", choices=["", "genesun", "galirax", "zevopel"],
+                    help="instead of the default workload: prefill / decode of this design at real layer shapes beside the closest existing model at equal size")
+    ap.add_argument("--design-sizes", default="", help="comma-separated subset of the sizes of the design (genesun: " + ",".join(DESIGN_SIZES) + "; the others: " + ",".join(GALIRAX_SIZES) + ")")
     args = ap.parse_args()
     if args.design:
         return design_leg(args)
