@@ -129,7 +129,8 @@ enum b200_ext_op {
                                   op_params: [2] n_group, [3] n_group_used, [4] scale, [5] n_used, [6] enum b200_router_score, [7] weights are the
                                   scores as they are (no division by their sum) */
     B200_EXT_SILU_MUL = 13,    /* src: a, b: dst = act(a) * b, any strides; op_params: [2] enum b200_glu_kind (0: silu), [3] limit, [4] alpha */
-    B200_EXT_MOE_COMBINE = 14, /* src: y [n, n_used, T], weights [n_used, T], add0, add1 (optional [n, T]): dst = add0 + add1 + sum_k w_k y_k */
+    B200_EXT_MOE_COMBINE = 14, /* src: y [n, n_used, T], weights [n_used, T], add0, add1 (optional [n, T]), [norm weight [n]]: dst = add0 + add1 + sum_k w_k y_k;
+                                  op_params[2] != 0: an RMS norm with eps op_params[3] and the norm weight runs over the sum before add0 joins (no add1) */
     B200_EXT_UNARY = 15,       /* src: x; op_params: [2] enum b200_unary_op, [3] p0, [4] p1 */
     B200_EXT_MUL_MAT_ID = 16,  /* src: experts [K, M, E] f32 / bf16, b [K, n_b_rows, T], ids [n_used, T]: dense-weight form of MUL_MAT_ID */
 };
@@ -294,6 +295,12 @@ B200_API int b200_op_moe_route_scored(const float *logits, int64_t ld_logits, co
  * optional); strides in floats. */
 B200_API int b200_op_moe_combine(const float *y, int64_t y_s_slot, int64_t y_s_tok, const float *w, int64_t w_s_tok, const float *add0, int64_t add0_stride,
                                  const float *add1, int64_t add1_stride, float *dst, int64_t dst_stride, int64_t n, int32_t n_used, int64_t n_tok, b200_stream_t stream);
+
+/* The same sum followed by an RMS norm over it and a residual: dst[t] = res[t] + s / sqrt(mean(s^2) + eps) * norm_w with s = sum_k w[t][k] * y[t][k];
+ * norm_w and res are optional; n <= B200_MOE_COMBINE_NORM_MAX (the summed row waits in shared memory). */
+#define B200_MOE_COMBINE_NORM_MAX 16384
+B200_API int b200_op_moe_combine_norm(const float *y, int64_t y_s_slot, int64_t y_s_tok, const float *w, int64_t w_s_tok, const float *norm_w, float eps, const float *res,
+                                      int64_t res_stride, float *dst, int64_t dst_stride, int64_t n, int32_t n_used, int64_t n_tok, b200_stream_t stream);
 
 /* MUL_MAT_ID over dense f32 or bf16 expert matrices: as [K, M, n_expert], b [K, n_b_rows, T] f32, ids [n_used, T]:
  * dst[:, s, t] = as[:, :, ids[s, t]] . b[:, s % n_b_rows, t].  Any K and M; f32 accumulation; products in f32 (bf16 weights are

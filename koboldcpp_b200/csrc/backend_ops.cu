@@ -85,7 +85,8 @@ static bool ext_op_supported(const ggml_tensor *op) {
         case B200_EXT_SILU_MUL:
             return s[0] && s[1] && s[0]->type == GGML_TYPE_F32 && s[1]->type == GGML_TYPE_F32 && op->type == GGML_TYPE_F32 && same_shape(s[0], op) && same_shape(s[1], op);
         case B200_EXT_MOE_COMBINE:
-            return f32_rows(s[0]) && f32_rows(s[1]) && (!s[2] || f32_rows(s[2])) && (!s[3] || f32_rows(s[3])) && f32_rows(op) && s[0]->nb[1] == 4 * (size_t)s[0]->ne[0];
+            return f32_rows(s[0]) && f32_rows(s[1]) && (!s[2] || f32_rows(s[2])) && (!s[3] || f32_rows(s[3])) && f32_rows(op) && s[0]->nb[1] == 4 * (size_t)s[0]->ne[0] &&
+                   (!op->op_params[2] || (!s[3] && op->ne[0] <= B200_MOE_COMBINE_NORM_MAX && (!s[4] || (f32_vec(s[4]) && s[4]->ne[0] == op->ne[0]))));
         case B200_EXT_UNARY:
             return s[0] && s[0]->type == GGML_TYPE_F32 && op->type == GGML_TYPE_F32 && is_contiguous(s[0]) && is_contiguous(op);
         case B200_EXT_MUL_MAT_ID:
@@ -243,6 +244,12 @@ static void run_ext(ExecCtx &x, const ggml_tensor *n) {
             break;
         }
         case B200_EXT_MOE_COMBINE:
+            if (n->op_params[2]) {
+                B200_CHECK_RC(b200_op_moe_combine_norm((const float *)s[0]->data, (int64_t)(s[0]->nb[1] / 4), (int64_t)(s[0]->nb[2] / 4), (const float *)s[1]->data, (int64_t)(s[1]->nb[1] / 4),
+                                                       s[4] ? (const float *)s[4]->data : nullptr, ext_f(n, 3), s[2] ? (const float *)s[2]->data : nullptr,
+                                                       s[2] ? (int64_t)(s[2]->nb[1] / 4) : 0, (float *)n->data, (int64_t)(n->nb[1] / 4), n->ne[0], (int32_t)s[0]->ne[1], n->ne[1], x.stream));
+                break;
+            }
             B200_CHECK_RC(b200_op_moe_combine((const float *)s[0]->data, (int64_t)(s[0]->nb[1] / 4), (int64_t)(s[0]->nb[2] / 4), (const float *)s[1]->data, (int64_t)(s[1]->nb[1] / 4),
                                               s[2] ? (const float *)s[2]->data : nullptr, s[2] ? (int64_t)(s[2]->nb[1] / 4) : 0, s[3] ? (const float *)s[3]->data : nullptr,
                                               s[3] ? (int64_t)(s[3]->nb[1] / 4) : 0, (float *)n->data, (int64_t)(n->nb[1] / 4), n->ne[0], (int32_t)s[0]->ne[1], n->ne[1], x.stream));

@@ -13,7 +13,8 @@
 // Graph choices: q, k, v and the head gates are ONE product over row-concatenated weights (rows padded to a multiple of 8 so that
 // every slice of the result starts 16-byte aligned when the sizes allow it); gate and up are one product; per-head norm, rotation
 // and the cache store are one launch; sink, chunks and the head gate live inside the attention kernels; c * a * (1 + w) is folded
-// into ONE weight vector per norm when the model is finalised, so "norm, scale, add to the stream" is one launch; the embedding
+// into ONE weight vector per norm when the model is finalised, so "norm, scale, add to the stream" is one launch (behind the
+// experts the weighted sum over the chosen ones is part of that launch too); the embedding
 // scale is folded into the f32 table; the router is an f32 product of f32 weights with the unrounded stream in every mode.
 #include "host_fused.h"
 
@@ -330,8 +331,13 @@ int zv_build(b200_llama *m, const BatchShape &bs) {
             ggml_tensor *gu = b.ext(b.alloc_result(GGML_TYPE_F32, 2 * F, NU, T), B200_EXT_MUL_MAT_ID, {L.gate_up, b.reshape(x, W, 1, T), ids});
             ggml_tensor *act = glu(b.alloc_result(GGML_TYPE_F32, F, NU, T), b.view_3d(gu, F, NU, T, gu->nb[1], gu->nb[2], 0), b.view_3d(gu, F, NU, T, gu->nb[1], gu->nb[2], (size_t)F * 4), lp);
             ggml_tensor *dn = b.ext(b.alloc_result(GGML_TYPE_F32, W, NU, T), B200_EXT_MUL_MAT_ID, {L.down, act, ids});
-            ggml_tensor *ff = b.ext(b.alloc_result(GGML_TYPE_F32, W, T), B200_EXT_MOE_COMBINE, {dn, wts, nullptr, nullptr});
-            x = post_norm(ff, L.post2, x);
+            if (W <= B200_MOE_COMBINE_NORM_MAX) {  // the weighted sum over the chosen experts, the norm behind it and the residual in one launch
+                ggml_tensor *nx = b.ext(b.alloc_result(GGML_TYPE_F32, W, T), B200_EXT_MOE_COMBINE, {dn, wts, x, nullptr, L.post2});
+                nx->op_params[2] = 1; Builder::set_f(nx, 3, eps);
+                x = nx;
+            } else {
+                x = post_norm(b.ext(b.alloc_result(GGML_TYPE_F32, W, T), B200_EXT_MOE_COMBINE, {dn, wts, nullptr, nullptr}), L.post2, x);
+            }
         }
     }
     b.bump = &m->regions[R_TAIL];

@@ -210,6 +210,30 @@ __global__ void moe_combine_kernel(const float *__restrict__ y, int64_t y_s_slot
     dst[t * dst_stride + i] = s;
 }
 
+// The weighted sum of a token's expert results, an RMS norm over it with a weight, and the residual stream, one CTA per token:
+// the summed row waits in shared memory between the statistics and the output.
+__global__ void __launch_bounds__(256) moe_combine_norm_kernel(const float *__restrict__ y, int64_t y_s_slot, int64_t y_s_tok, const float *__restrict__ w, int64_t w_s_tok,
+                                                               const float *__restrict__ nw, float eps, const float *__restrict__ res, int64_t res_stride,
+                                                               float *__restrict__ dst, int64_t dst_stride, int n, int n_used) {
+    extern __shared__ float row[];
+    __shared__ float sh[32];
+    const int64_t t = blockIdx.x;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        float s = 0.f;
+        for (int k = 0; k < n_used; k++) s += w[t * w_s_tok + k] * y[t * y_s_tok + k * y_s_slot + i];
+        row[i] = s;
+        ss += s * s;
+    }
+    const float scale = 1.0f / sqrtf(block_sum(ss, sh) / (float)n + eps);
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        float v = row[i] * scale;
+        if (nw) v *= nw[i];
+        if (res) v += res[t * res_stride + i];
+        dst[t * dst_stride + i] = v;
+    }
+}
+
 static unsigned grid1d(int64_t n, int block) { return (unsigned)((n + block - 1) / block); }
 
 }  // namespace b200
@@ -281,6 +305,19 @@ extern "C" int b200_op_glu_strided(int kind, const b200_tensor *a, const b200_te
     if (kind == B200_GLU_GELU_TANH) glu_strided_kernel<B200_GLU_GELU_TANH><<<grid1d(n, 256), 256, 0, st>>>(td(a), td(b), td(dst), n, limit, alpha);
     else if (kind == B200_GLU_SWISH_CLAMPED) glu_strided_kernel<B200_GLU_SWISH_CLAMPED><<<grid1d(n, 256), 256, 0, st>>>(td(a), td(b), td(dst), n, limit, alpha);
     else glu_strided_kernel<B200_GLU_SILU><<<grid1d(n, 256), 256, 0, st>>>(td(a), td(b), td(dst), n, limit, alpha);
+    B200_CUDA_TRY(cudaGetLastError());
+    return B200_OK;
+}
+
+extern "C" int b200_op_moe_combine_norm(const float *y, int64_t y_s_slot, int64_t y_s_tok, const float *w, int64_t w_s_tok, const float *norm_w, float eps, const float *res,
+                                        int64_t res_stride, float *dst, int64_t dst_stride, int64_t n, int32_t n_used, int64_t n_tok, b200_stream_t stream) {
+    OPX_REQUIRE(y && w && dst && n >= 0 && n <= B200_MOE_COMBINE_NORM_MAX && n_used > 0 && n_tok >= 0, B200_ERR_INVALID, "b200_op_moe_combine_norm: bad argument (rows of at most %d values)",
+                B200_MOE_COMBINE_NORM_MAX);
+    if (n == 0 || n_tok == 0) return B200_OK;
+    if ((size_t)n * sizeof(float) > 40 * 1024)  // beyond what a kernel gets without asking
+        B200_CUDA_TRY(cudaFuncSetAttribute(moe_combine_norm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(B200_MOE_COMBINE_NORM_MAX * sizeof(float))));
+    moe_combine_norm_kernel<<<(unsigned)n_tok, 256, (size_t)n * sizeof(float), (cudaStream_t)stream>>>(y, y_s_slot, y_s_tok, w, w_s_tok, norm_w, eps, res, res_stride, dst, dst_stride,
+                                                                                                       (int)n, n_used);
     B200_CUDA_TRY(cudaGetLastError());
     return B200_OK;
 }

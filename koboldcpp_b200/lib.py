@@ -191,6 +191,8 @@ _OPS_SIGS = {
     "b200_op_glu_strided": (C.c_int, [C.c_int, C.POINTER(Tensor), C.POINTER(Tensor), C.POINTER(Tensor), C.c_float, C.c_float, C.c_void_p]),
     "b200_op_moe_combine": (C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64,
                                       C.c_int64, C.c_int32, C.c_int64, C.c_void_p]),
+    "b200_op_moe_combine_norm": (C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_float, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64,
+                                           C.c_int64, C.c_int32, C.c_int64, C.c_void_p]),
     "b200_op_mul_mat_id_float": (C.c_int, [C.POINTER(Tensor), C.POINTER(Tensor), C.POINTER(Tensor), C.POINTER(Tensor), C.c_void_p]),
 }
 

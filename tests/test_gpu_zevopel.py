@@ -235,6 +235,19 @@ def test_gated_activations_gelu_and_clamped_swish():
     assert rel(dact.to_numpy(np.float32, (T, NU, F)), a * R.sigmoid(a) * u) < 2e-6
 
 
+@pytest.mark.parametrize("n,NU,T", [(40, 3, 7), (70, 1, 2), (1024, 2, 5), (12288, 4, 2), (16384, 2, 3)])
+def test_expert_sum_norm_and_residual_in_one_launch(n, NU, T):
+    rng = np.random.default_rng(n + NU)
+    y, w, res, nw = rng.standard_normal((T, NU, n)) * 2, rng.random((T, NU)), rng.standard_normal((T, n)), 1 + 0.3 * rng.standard_normal(n)
+    eps = 1e-6
+    dy, dw, dr, dn, dout = dev(y), dev(w), dev(res), dev(nw), H.DeviceBuffer(4 * T * n + 256)
+    check(lib().b200_op_moe_combine_norm(dy.ptr, n, NU * n, dw.ptr, NU, dn.ptr, eps, dr.ptr, n, dout.ptr, n, n, NU, T, None))
+    s = np.einsum("tk,tkn->tn", w, y)
+    assert rel(dout.to_numpy(np.float32, (T, n)), res + R.rms_norm_plain(s, nw, eps)) < 3e-6
+    check(lib().b200_op_moe_combine_norm(dy.ptr, n, NU * n, dw.ptr, NU, None, eps, None, 0, dout.ptr, n, n, NU, T, None))
+    assert rel(dout.to_numpy(np.float32, (T, n)), R.rms_unit(s, eps)) < 3e-6
+
+
 def test_clamped_expert_matches_its_parts():
     rng = np.random.default_rng(5)
     x, Wg, Wu, Wd = rng.standard_normal(12) * 2, rng.standard_normal((7, 12)), rng.standard_normal((7, 12)), rng.standard_normal((12, 7))
