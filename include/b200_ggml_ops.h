@@ -297,7 +297,7 @@ B200_API int b200_op_moe_combine(const float *y, int64_t y_s_slot, int64_t y_s_t
                                  const float *add1, int64_t add1_stride, float *dst, int64_t dst_stride, int64_t n, int32_t n_used, int64_t n_tok, b200_stream_t stream);
 
 /* The same sum followed by an RMS norm over it and a residual: dst[t] = res[t] + s / sqrt(mean(s^2) + eps) * norm_w with s = sum_k w[t][k] * y[t][k];
- * norm_w and res are optional; n <= B200_MOE_COMBINE_NORM_MAX (the summed row waits in shared memory). */
+ * norm_w and res are optional; n <= B200_MOE_COMBINE_NORM_MAX (the summed row waits in the registers of one CTA), n_used <= 32. */
 #define B200_MOE_COMBINE_NORM_MAX 16384
 B200_API int b200_op_moe_combine_norm(const float *y, int64_t y_s_slot, int64_t y_s_tok, const float *w, int64_t w_s_tok, const float *norm_w, float eps, const float *res,
                                       int64_t res_stride, float *dst, int64_t dst_stride, int64_t n, int32_t n_used, int64_t n_tok, b200_stream_t stream);

@@ -210,27 +210,42 @@ __global__ void moe_combine_kernel(const float *__restrict__ y, int64_t y_s_slot
     dst[t * dst_stride + i] = s;
 }
 
-// The weighted sum of a token's expert results, an RMS norm over it with a weight, and the residual stream, one CTA per token:
-// the summed row waits in shared memory between the statistics and the output.
-__global__ void __launch_bounds__(256) moe_combine_norm_kernel(const float *__restrict__ y, int64_t y_s_slot, int64_t y_s_tok, const float *__restrict__ w, int64_t w_s_tok,
-                                                               const float *__restrict__ nw, float eps, const float *__restrict__ res, int64_t res_stride,
-                                                               float *__restrict__ dst, int64_t dst_stride, int n, int n_used) {
-    extern __shared__ float row[];
-    __shared__ float sh[32];
+// The weighted sum of a token's expert results, an RMS norm over it with a weight, and the residual stream, one CTA per token.
+// The summed row stays in registers (VPT values per thread) between the statistics and the output, and every load of a thread
+// -- expert rows, norm weight, residual -- is issued before the block-wide sum, so a token costs one trip to memory.
+template <int VPT>
+__global__ void __launch_bounds__(1024) moe_combine_norm_kernel(const float *__restrict__ y, int64_t y_s_slot, int64_t y_s_tok, const float *__restrict__ w, int64_t w_s_tok,
+                                                                const float *__restrict__ nw, float eps, const float *__restrict__ res, int64_t res_stride,
+                                                                float *__restrict__ dst, int64_t dst_stride, int n, int n_used) {
+    __shared__ float sh[32], sw[32];
     const int64_t t = blockIdx.x;
-    float ss = 0.f;
-    for (int i = threadIdx.x; i < n; i += blockDim.x) {
-        float s = 0.f;
-        for (int k = 0; k < n_used; k++) s += w[t * w_s_tok + k] * y[t * y_s_tok + k * y_s_slot + i];
-        row[i] = s;
-        ss += s * s;
+    if ((int)threadIdx.x < n_used) sw[threadIdx.x] = w[t * w_s_tok + threadIdx.x];
+    __syncthreads();
+    float v[VPT], wv[VPT], rv[VPT];
+#pragma unroll
+    for (int k = 0; k < VPT; k++) {
+        const int i = threadIdx.x + k * blockDim.x;
+        v[k] = 0.f;
+        wv[k] = (nw && i < n) ? nw[i] : 1.f;
+        rv[k] = (res && i < n) ? res[t * res_stride + i] : 0.f;
     }
+    for (int kk = 0; kk < n_used; kk++) {
+        const float wk = sw[kk];
+        const float *yk = y + t * y_s_tok + kk * y_s_slot;
+#pragma unroll
+        for (int k = 0; k < VPT; k++) {
+            const int i = threadIdx.x + k * blockDim.x;
+            if (i < n) v[k] += wk * yk[i];
+        }
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < VPT; k++) ss += v[k] * v[k];
     const float scale = 1.0f / sqrtf(block_sum(ss, sh) / (float)n + eps);
-    for (int i = threadIdx.x; i < n; i += blockDim.x) {
-        float v = row[i] * scale;
-        if (nw) v *= nw[i];
-        if (res) v += res[t * res_stride + i];
-        dst[t * dst_stride + i] = v;
+#pragma unroll
+    for (int k = 0; k < VPT; k++) {
+        const int i = threadIdx.x + k * blockDim.x;
+        if (i < n) dst[t * dst_stride + i] = v[k] * scale * wv[k] + rv[k];
     }
 }
 
@@ -314,10 +329,11 @@ extern "C" int b200_op_moe_combine_norm(const float *y, int64_t y_s_slot, int64_
     OPX_REQUIRE(y && w && dst && n >= 0 && n <= B200_MOE_COMBINE_NORM_MAX && n_used > 0 && n_tok >= 0, B200_ERR_INVALID, "b200_op_moe_combine_norm: bad argument (rows of at most %d values)",
                 B200_MOE_COMBINE_NORM_MAX);
     if (n == 0 || n_tok == 0) return B200_OK;
-    if ((size_t)n * sizeof(float) > 40 * 1024)  // beyond what a kernel gets without asking
-        B200_CUDA_TRY(cudaFuncSetAttribute(moe_combine_norm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(B200_MOE_COMBINE_NORM_MAX * sizeof(float))));
-    moe_combine_norm_kernel<<<(unsigned)n_tok, 256, (size_t)n * sizeof(float), (cudaStream_t)stream>>>(y, y_s_slot, y_s_tok, w, w_s_tok, norm_w, eps, res, res_stride, dst, dst_stride,
-                                                                                                       (int)n, n_used);
+    OPX_REQUIRE(n_used <= 32, B200_ERR_UNSUPPORTED, "b200_op_moe_combine_norm: at most 32 experts per token");
+    const int rb = n <= 512 ? 128 : n <= 1024 ? 256 : n <= 2048 ? 512 : 1024, vpt = (int)((n + rb - 1) / rb);
+#define B200_MCN(V) moe_combine_norm_kernel<V><<<(unsigned)n_tok, rb, 0, (cudaStream_t)stream>>>(y, y_s_slot, y_s_tok, w, w_s_tok, norm_w, eps, res, res_stride, dst, dst_stride, (int)n, n_used)
+    if (vpt <= 4) B200_MCN(4); else if (vpt <= 8) B200_MCN(8); else B200_MCN(16);
+#undef B200_MCN
     B200_CUDA_TRY(cudaGetLastError());
     return B200_OK;
 }
