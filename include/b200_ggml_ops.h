@@ -111,7 +111,8 @@ B200_API int b200_op_mul_mat_float(const b200_tensor *w, const b200_tensor *x, c
  * Everything here is computed in f32. */
 #define B200_EXT_TAG 0xB200E7A5u
 enum b200_ext_op {
-    B200_EXT_NORM = 1,         /* src: x, w, [gate, gate_bias, res, bias]; op_params: [2] kind, [3] eps, [4] w_period, [5] gate on the output */
+    B200_EXT_NORM = 1,         /* src: x, w, [gate, gate_bias, res, bias]; op_params: [2] kind, [3] eps, [4] w_period, [5] gate: 0 sigmoid in front of the norm,
+                                  1 sigmoid on the output, 2 silu on the output */
     B200_EXT_POLYNORM = 2,     /* src: x, coef[4]; op_params: [3] eps */
     B200_EXT_ROPE_TABLE = 3,   /* src: x, pos, freqs; in place; op_params: [2] n_dims, [3] mscale, [4] neox */
     B200_EXT_WEIGHTED_SUM = 4, /* src: xs [n, J], w [J] */
@@ -121,19 +122,32 @@ enum b200_ext_op {
     B200_EXT_MLSTM_SCAN = 8,   /* src: q, k, v, ig, fg, i_bias, f_bias, seq_info, state; op_params: [2] heads, [3] dim, [4] vdim, [5] gate_cap */
     B200_EXT_QKV_STORE = 9,    /* src: q, k, v, vecs (the present ones of q.b, k.b, v.b, q.norm, k.norm packed in one tensor, or NULL), pos, freqs,
                                   cells, k cache, v cache; q in place; op_params: [2] dim, [3] vdim, [4] n_dims, [5] eps, [6] biases present, [7] norms present
-                                  (1: over the whole row, 2: per head with one weight vector of dim values), [8] pairs are (i, i + n_dims / 2) */
+                                  (1: over the whole row, 2: per head with one weight vector of dim values), [8] pairs are (i, i + n_dims / 2), [9] every head of v is divided
+                                  by its root mean square, [10] q temperature coefficient, [11] its period in positions; freqs may be NULL without rotation */
     B200_EXT_SINK_ATTN = 10,   /* src: q, k cache, v cache, sink, tok_seq, tok_pos, cell_seq, cell_pos, [head gate [heads, T]]; op_params: [2] dim, [3] scale,
-                                  [4] window, [5] keep_first, [6] bf16 products, [7] vdim, [8] chunk */
+                                  [4] window, [5] keep_first, [6] bf16 products, [7] vdim, [8] chunk, [9] enum b200_attn_weights; src[9]: score bias by distance
+                                  [heads, n_dist] (optional) */
     B200_EXT_LINEAR_ATTN_SCAN = 11, /* src: q, k, v, decay, seq_info, state; op_params: [2] heads, [3] dim, [4] vdim, [5] silu on q / k / v */
     B200_EXT_MOE_ROUTE = 12,   /* src: logits, correction; dst [2 n_used, T]: per token n_used weights (f32), then n_used expert ids (i32);
                                   op_params: [2] n_group, [3] n_group_used, [4] scale, [5] n_used, [6] enum b200_router_score, [7] weights are the
                                   scores as they are (no division by their sum) */
-    B200_EXT_SILU_MUL = 13,    /* src: a, b: dst = act(a) * b, any strides; op_params: [2] enum b200_glu_kind (0: silu), [3] limit, [4] alpha */
+    B200_EXT_SILU_MUL = 13,    /* src: a, b, [scale [ne1, ne2]]: dst = act(s a) * (s b), any strides; op_params: [2] enum b200_glu_kind (0: silu), [3] limit, [4] alpha */
     B200_EXT_MOE_COMBINE = 14, /* src: y [n, n_used, T], weights [n_used, T], add0, add1 (optional [n, T]), [norm weight [n]]: dst = add0 + add1 + sum_k w_k y_k;
-                                  op_params[2] != 0: an RMS norm with eps op_params[3] and the norm weight runs over the sum before add0 joins (no add1) */
+                                  op_params[2] != 0: an RMS norm with eps op_params[3] and the norm weight runs over the sum before add0 joins (no add1);
+                                  else src[5], src[6] (optional): a shared result [n, T] and its gate logit per token, and op_params[4] the multiplier (0 reads
+                                  as 1): dst = add0 + mult * (add1 + sum_k w_k y_k + sigmoid(gate) * shared); y and the weights may be absent */
     B200_EXT_UNARY = 15,       /* src: x; op_params: [2] enum b200_unary_op, [3] p0, [4] p1 */
     B200_EXT_MUL_MAT_ID = 16,  /* src: experts [K, M, E] f32 / bf16, b [K, n_b_rows, T], ids [n_used, T]: dense-weight form of MUL_MAT_ID */
+    B200_EXT_ADD_SINUSOID = 17, /* src: x [n, T], pos, freqs [ceil(n / 2)]: dst[2i] = x[2i] + sin(pos f_i), dst[2i + 1] = x[2i + 1] + cos(pos f_i) */
+    B200_EXT_SHORT_CONV = 18,  /* src: x [channels, T], w [taps, channels], bias (optional), seq_info, tail [(taps - 1) * channels, slots]; op_params: [2] activation
+                                  (0 none, 1 silu) */
+    B200_EXT_DELTA_RULE_SCAN = 19, /* src: q, k, v, a, b, a_log, dt_bias, seq_info, state; op_params: [2] heads, [3] kv_heads, [4] dim, [5] vdim, [6] q and k become
+                                  unit vectors, [7] the eps of that, [8] q scale */
+    B200_EXT_MINGRU_SCAN = 20, /* src: z, x, g (optional), z bias, x bias (optional), seq_info, state [width, slots] */
 };
+/* how attention turns scores into weights: SOFTMAX over the visible keys (with the sink in the denominator), or SIGMOID of every score by
+ * itself with no normalisation over the keys (a sink has no meaning then) */
+enum b200_attn_weights { B200_ATTN_SOFTMAX = 0, B200_ATTN_SIGMOID = 1 };
 
 enum b200_router_score { B200_ROUTER_SIGMOID = 0, B200_ROUTER_SOFTMAX = 1 /* over all experts */ };
 /* gated activations dst = f(a, b): SILU a sigmoid(a) b; GELU_TANH gelu(a) b with the tanh form of gelu; SWISH_CLAMPED with g = min(a, limit),
@@ -148,7 +162,8 @@ B200_API int b200_op_norm(const b200_tensor *x, const float *w, int64_t w_period
                           const b200_tensor *res, const b200_tensor *dst, float eps, int kind, b200_stream_t stream);
 
 /* The same with a bias behind the weight (dst = res + N(..) * w + bias) and the gate either in front of the norm (gate_on_output
- * == 0, as above) or behind it: dst = res + (N(x) * w + bias) * sigmoid(gate + gate_bias). */
+ * == 0, as above) or behind it: dst = res + (N(x) * w + bias) * f(gate + gate_bias), f the sigmoid (gate_on_output == 1) or silu
+ * z sigmoid(z) (gate_on_output == 2). */
 B200_API int b200_op_norm_affine(const b200_tensor *x, const float *w, int64_t w_period, const float *bias, const b200_tensor *gate, const float *gate_bias,
                                  int gate_on_output, const b200_tensor *res, const b200_tensor *dst, float eps, int kind, b200_stream_t stream);
 
@@ -218,6 +233,10 @@ B200_API int b200_op_mlstm_scan(const b200_mlstm_args *a, b200_stream_t stream);
 B200_API int b200_op_silu_mul_strided(const b200_tensor *a, const b200_tensor *b, const b200_tensor *dst, b200_stream_t stream);
 /* The same for any enum b200_glu_kind; limit and alpha are read by B200_GLU_SWISH_CLAMPED only. */
 B200_API int b200_op_glu_strided(int kind, const b200_tensor *a, const b200_tensor *b, const b200_tensor *dst, float limit, float alpha, b200_stream_t stream);
+/* The same with both inputs multiplied by scale[i1, i2] first (f32, any strides; NULL: none): an expert whose weight scales its input,
+ * applied behind the linear gate / up products instead of in front of them. */
+B200_API int b200_op_glu_scaled(int kind, const b200_tensor *a, const b200_tensor *b, const b200_tensor *scale, const b200_tensor *dst, float limit, float alpha,
+                                b200_stream_t stream);
 
 /* Softmax attention of n_head query heads over cached keys and values of n_head_kv heads (query head h reads kv head
  * h / (n_head / n_head_kv)); one cache row per cell holds all kv heads of a token: k rows [n_head_kv * dim], v rows
@@ -239,10 +258,13 @@ typedef struct {
     int32_t n_head, n_head_kv, dim, vdim, n_dims, n_tokens;
     float eps;
     int32_t norm_per_head, rope_halves;
+    int32_t v_unit_rms;                    /* 1: every head of v is divided by sqrt(mean(v^2) + eps) before it is stored (behind the bias) */
+    float   q_temp_coef;                   /* != 0: q is multiplied by 1 + coef * ln(floor((pos + 1) / q_temp_every) + 1) */
+    int32_t q_temp_every;
 } b200_qkv_store_args;
 B200_API int b200_op_qkv_store(const b200_qkv_store_args *a, b200_stream_t stream);
 
-/* score = scale * q . k; a token sees the cells of its own sequence with cell_pos <= tok_pos and (window == 0 or
+/* score = scale * q . k (+ dist_bias, see below); a token sees the cells of its own sequence with cell_pos <= tok_pos and (window == 0 or
  * tok_pos - cell_pos < window or cell_pos < keep_first) and (chunk == 0 or tok_pos / chunk == cell_pos / chunk: positions are cut
  * into chunks counted from 0 and nothing is seen across a cut); softmax in f32 whose denominator also holds exp(sink[h]) when
  * sink != NULL (the sink has no key and no value).  gate != NULL: head h of token t is multiplied by sigmoid(gate[t * gate_stride
@@ -259,6 +281,8 @@ typedef struct {
     int32_t bf16_products;
     int32_t chunk;
     const float *gate; int64_t gate_stride;
+    int32_t weights;                       /* enum b200_attn_weights */
+    const float *dist_bias; int32_t n_dist; /* [n_dist][n_head] added to the scaled score of a key min(tok_pos - cell_pos, n_dist - 1) positions back (NULL: none) */
 } b200_sink_attn_args;
 B200_API int b200_op_sink_attn(const b200_sink_attn_args *a, b200_stream_t stream);
 /* The same with a workspace of b200_sink_attn_workspace_bytes(a) bytes (16-byte aligned; 0: none needed): with few tokens and
@@ -296,6 +320,13 @@ B200_API int b200_op_moe_route_scored(const float *logits, int64_t ld_logits, co
 B200_API int b200_op_moe_combine(const float *y, int64_t y_s_slot, int64_t y_s_tok, const float *w, int64_t w_s_tok, const float *add0, int64_t add0_stride,
                                  const float *add1, int64_t add1_stride, float *dst, int64_t dst_stride, int64_t n, int32_t n_used, int64_t n_tok, b200_stream_t stream);
 
+/* dst[t] = add0[t] + mult * (add1[t] + sum_k w[t][k] * y[t][k] + sigmoid(gate[t * gate_stride]) * shared[t]): the chosen experts, a shared
+ * expert gated per token, the other sublayer's result and the scaled residual connection in one launch.  w NULL: weights of one; y
+ * NULL (n_used 0), add0, add1, shared: optional. */
+B200_API int b200_op_moe_combine_shared(const float *y, int64_t y_s_slot, int64_t y_s_tok, const float *w, int64_t w_s_tok, const float *add0, int64_t add0_stride,
+                                        const float *add1, int64_t add1_stride, const float *shared, int64_t shared_stride, const float *gate, int64_t gate_stride,
+                                        float mult, float *dst, int64_t dst_stride, int64_t n, int32_t n_used, int64_t n_tok, b200_stream_t stream);
+
 /* The same sum followed by an RMS norm over it and a residual: dst[t] = res[t] + s / sqrt(mean(s^2) + eps) * norm_w with s = sum_k w[t][k] * y[t][k];
  * norm_w and res are optional; n <= B200_MOE_COMBINE_NORM_MAX (the summed row waits in the registers of one CTA), n_used <= 32. */
 #define B200_MOE_COMBINE_NORM_MAX 16384
@@ -306,6 +337,55 @@ B200_API int b200_op_moe_combine_norm(const float *y, int64_t y_s_slot, int64_t 
  * dst[:, s, t] = as[:, :, ids[s, t]] . b[:, s % n_b_rows, t].  Any K and M; f32 accumulation; products in f32 (bf16 weights are
  * widened).  The batched tensor-core form for bf16 weights is b200_mul_mat_id_q (b200_ggml.h). */
 B200_API int b200_op_mul_mat_id_float(const b200_tensor *as, const b200_tensor *b, const b200_tensor *ids, const b200_tensor *dst, b200_stream_t stream);
+
+/* dst[t][2i] = x[t][2i] + sin(pos[t] * freqs[i]), dst[t][2i + 1] = x[t][2i + 1] + cos(pos[t] * freqs[i]); x, dst [n, T] f32 rows with any
+ * row strides (they may be the same); angles pos * f in f32. */
+B200_API int b200_op_add_sinusoid(const b200_tensor *x, const int32_t *pos, const float *freqs, const b200_tensor *dst, b200_stream_t stream);
+
+/* Short causal convolution over time, every channel by itself: y[t] = act(sum_j w[c][j] * u[t - taps + 1 + j]), u = x + bias, zeros before
+ * the start of a sequence.  The last taps - 1 values of u of a sequence wait in its slot of `tail` ([taps - 1][channels] per slot) for
+ * its next tokens.  seq_info as for b200_op_mlstm_scan.  x, dst [n_tokens][channels] (not the same memory), strides in floats; w
+ * [channels][taps]; taps <= 33. */
+typedef struct {
+    const float *x; int64_t x_stride;
+    const float *bias;                     /* [channels] or NULL */
+    const float *w;
+    const int32_t *seq_info; int32_t n_seq;
+    float *tail; int64_t slot_stride;
+    float *dst; int64_t dst_stride;
+    int32_t channels, taps, act;           /* act: 0 none, 1 silu */
+    int32_t n_tokens;
+} b200_short_conv_args;
+B200_API int b200_op_short_conv(const b200_short_conv_args *a, b200_stream_t stream);
+
+/* Gated delta rule over the tokens of n_seq sequences, a state S [dim, vdim] per (slot, head) in f32:
+ *   g = exp(-exp(a_log[h]) * softplus(a[t][h] + dt_bias[h])),  beta = sigmoid(b[t][h]),
+ *   S <- g S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q.
+ * Head h reads q / k head h / (heads / kv_heads).  With unit_qk, q and k are first divided by sqrt(sum(x^2) + unit_eps) per head; q is
+ * multiplied by q_scale.  State [head][vdim][dim] per slot; seq_info as for b200_op_mlstm_scan; strides in floats. */
+typedef struct {
+    const float *q, *k, *v; int64_t q_stride, k_stride, v_stride;  /* q, k [n_tokens][kv_heads * dim], v [n_tokens][heads * vdim] */
+    const float *a, *b; int64_t a_stride, b_stride;                /* [n_tokens][heads] */
+    const float *a_log, *dt_bias;                                  /* [heads] */
+    const int32_t *seq_info; int32_t n_seq;
+    float *state; int64_t slot_stride;
+    float *dst; int64_t dst_stride;                                /* [n_tokens][heads * vdim] */
+    int32_t heads, kv_heads, dim, vdim, unit_qk;
+    float unit_eps, q_scale;
+} b200_delta_rule_args;
+B200_API int b200_op_delta_rule_scan(const b200_delta_rule_args *a, b200_stream_t stream);
+
+/* minGRU, element by element over `width` channels: zg = sigmoid(z + z_bias), u = x + x_bias, c = u + 1/2 where u >= 0 and sigmoid(u)
+ * elsewhere, S <- (1 - zg) S + zg c, dst = S * silu(g) (g NULL: dst = S).  State [width] per slot in f32; seq_info as above. */
+typedef struct {
+    const float *z, *x, *g; int64_t z_stride, x_stride, g_stride;
+    const float *z_bias, *x_bias;
+    const int32_t *seq_info; int32_t n_seq;
+    float *state; int64_t slot_stride;
+    float *dst; int64_t dst_stride;
+    int32_t width, n_tokens;
+} b200_mingru_args;
+B200_API int b200_op_mingru_scan(const b200_mingru_args *a, b200_stream_t stream);
 
 #ifdef __cplusplus
 }

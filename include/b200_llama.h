@@ -47,11 +47,13 @@ typedef struct {
     float   residual_mult;           /* architectures that scale a sublayer's result before it joins the residual stream (0 reads as 1) */
 } b200_llama_params;
 
-enum b200_arch { B200_ARCH_LLAMA = 0, B200_ARCH_GENESUN = 1, B200_ARCH_GALIRAX = 2, B200_ARCH_ZEVOPEL = 3 };
+enum b200_arch { B200_ARCH_LLAMA = 0, B200_ARCH_GENESUN = 1, B200_ARCH_GALIRAX = 2, B200_ARCH_ZEVOPEL = 3, B200_ARCH_MEDODRA = 4 };
 enum b200_mixer {
     B200_MIXER_LATENT_ATTENTION = 1, B200_MIXER_MLSTM = 2,
     B200_MIXER_ATTENTION = 3, /* softmax attention of heads over kv_heads cached keys / values, per-head sink, optional window */
     B200_MIXER_LIGHTNING = 4, /* linear attention: a decayed outer-product state per head */
+    B200_MIXER_DELTA = 5,     /* gated delta rule: the state forgets by a per-token decay and is corrected towards v along k */
+    B200_MIXER_SIGMOID_ATTENTION_GRU = 6, /* two mixers side by side: attention with sigmoid weights and a distance bias, and a minGRU */
 };
 enum b200_mlp {
     B200_MLP_NONE = 0, B200_MLP_DENSE_POLYNORM = 1, B200_MLP_MOE_GATED = 2 /* routed gated experts */,
@@ -98,6 +100,20 @@ typedef struct {
     float   glu_limit, glu_alpha;    /* B200_GLU_SWISH_CLAMPED */
     int32_t router_score;            /* enum b200_router_score */
     int32_t router_keep_scores;      /* 1: an expert's weight is its score, not divided by the sum over the chosen */
+    /* mixers with a short causal convolution over time on q, k, v (tensors "<leaf>.conv" [channels, taps]); the last taps - 1 inputs of a
+     * sequence are part of its state */
+    int32_t conv_taps;               /* 0 / 1: none */
+    /* B200_MIXER_SIGMOID_ATTENTION_GRU */
+    float   q_temp_coef;             /* queries are multiplied by 1 + coef * ln(floor((pos + 1) / q_temp_every) + 1) */
+    int32_t q_temp_every;
+    int32_t dist_bias_max;           /* the rows of the distance table "rel" [rows, heads]: distances below rows / 2 have a row each, the
+                                        others share the rest evenly in log distance up to this distance */
+    int32_t side_width;              /* size of the minGRU state */
+    /* feed-forward, further switches */
+    int32_t router_scale_input;      /* 1: a chosen expert's weight multiplies its input, not its result */
+    int32_t shared_ff;               /* > 0: a shared expert of this hidden size runs for every token ("mlp.shared.*"), times sigmoid(W_sg x) */
+    int32_t loop_input;              /* 1: every time this layer is about to run, the stream x is first replaced by W_in [x ; x0] ("loop.in" [width, 2 width]),
+                                        x0 being the stream as the embedding left it: the first layer of a looped stretch */
 } b200_layer_params;
 
 

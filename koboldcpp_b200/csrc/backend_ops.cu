@@ -70,27 +70,45 @@ static bool ext_op_supported(const ggml_tensor *op) {
             for (int i = 0; i < 5; i++) if (!f32_rows(s[i])) return false;
             return (!s[5] || f32_vec(s[5])) && (!s[6] || f32_vec(s[6])) && i32_vec(s[7]) && f32_rows(s[8]) && f32_rows(op) && op->op_params[3] <= 512;
         case B200_EXT_QKV_STORE:
-            return f32_rows(s[0]) && f32_rows(s[1]) && f32_rows(s[2]) && (!s[3] || f32_vec(s[3])) && i32_vec(s[4]) && f32_vec(s[5]) && i32_vec(s[6]) && f32_rows(s[7]) &&
+            return f32_rows(s[0]) && f32_rows(s[1]) && f32_rows(s[2]) && (!s[3] || f32_vec(s[3])) && i32_vec(s[4]) && (s[5] ? f32_vec(s[5]) : op->op_params[4] == 0) && i32_vec(s[6]) && f32_rows(s[7]) &&
                    f32_rows(s[8]) && op->op_params[2] > 0 && op->op_params[3] > 0 && s[0]->ne[0] % op->op_params[2] == 0 && s[1]->ne[0] % op->op_params[2] == 0 &&
                    s[2]->ne[0] % op->op_params[3] == 0 && s[1]->ne[0] / op->op_params[2] == s[2]->ne[0] / op->op_params[3];
         case B200_EXT_SINK_ATTN:
             return f32_rows(s[0]) && f32_rows(s[1]) && f32_rows(s[2]) && (!s[3] || f32_vec(s[3])) && i32_vec(s[4]) && i32_vec(s[5]) && i32_vec(s[6]) && i32_vec(s[7]) &&
                    f32_rows(op) && op->op_params[2] > 0 && op->op_params[2] <= 256 && op->op_params[7] > 0 && op->op_params[7] <= 256 && s[0]->ne[0] % op->op_params[2] == 0 &&
-                   (!s[8] || (f32_rows(s[8]) && s[8]->ne[0] == s[0]->ne[0] / op->op_params[2] && s[8]->ne[1] == s[0]->ne[1]));
+                   (!s[8] || (f32_rows(s[8]) && s[8]->ne[0] == s[0]->ne[0] / op->op_params[2] && s[8]->ne[1] == s[0]->ne[1])) &&
+                   (!s[9] || (f32_vec(s[9]) && s[9]->ne[0] == s[0]->ne[0] / op->op_params[2] && s[9]->ne[1] > 0));
         case B200_EXT_LINEAR_ATTN_SCAN:
             return f32_rows(s[0]) && f32_rows(s[1]) && f32_rows(s[2]) && f32_vec(s[3]) && i32_vec(s[4]) && f32_rows(s[5]) && f32_rows(op) && op->op_params[3] <= 256;
         case B200_EXT_MOE_ROUTE:
             return f32_rows(s[0]) && (!s[1] || f32_vec(s[1])) && f32_rows(op) && s[0]->ne[0] <= 256 && op->op_params[5] > 0 && op->op_params[5] <= 32 && op->ne[0] == 2 * op->op_params[5] &&
                    op->ne[1] == s[0]->ne[1];
         case B200_EXT_SILU_MUL:
-            return s[0] && s[1] && s[0]->type == GGML_TYPE_F32 && s[1]->type == GGML_TYPE_F32 && op->type == GGML_TYPE_F32 && same_shape(s[0], op) && same_shape(s[1], op);
+            return s[0] && s[1] && s[0]->type == GGML_TYPE_F32 && s[1]->type == GGML_TYPE_F32 && op->type == GGML_TYPE_F32 && same_shape(s[0], op) && same_shape(s[1], op) &&
+                   (!s[2] || (s[2]->type == GGML_TYPE_F32 && s[2]->ne[0] == op->ne[1] && s[2]->ne[1] == op->ne[2] && op->ne[3] == 1));
         case B200_EXT_MOE_COMBINE:
+            if (!op->op_params[2] && (s[5] || !s[0] || !s[1]))  // the form with a shared result: experts, weights, shared result and gate are all optional
+                return (!s[0] || f32_rows(s[0])) && (!s[1] || (s[0] && f32_rows(s[1]))) && (!s[2] || f32_rows(s[2])) && (!s[3] || f32_rows(s[3])) && (!s[5] || f32_rows(s[5])) &&
+                       (!s[6] || (s[5] && f32_rows(s[6]))) && f32_rows(op);
             return f32_rows(s[0]) && f32_rows(s[1]) && (!s[2] || f32_rows(s[2])) && (!s[3] || f32_rows(s[3])) && f32_rows(op) && s[0]->nb[1] == 4 * (size_t)s[0]->ne[0] &&
                    (!op->op_params[2] || (!s[3] && op->ne[0] <= B200_MOE_COMBINE_NORM_MAX && (!s[4] || (f32_vec(s[4]) && s[4]->ne[0] == op->ne[0]))));
         case B200_EXT_UNARY:
             return s[0] && s[0]->type == GGML_TYPE_F32 && op->type == GGML_TYPE_F32 && is_contiguous(s[0]) && is_contiguous(op);
         case B200_EXT_MUL_MAT_ID:
             return s[0] && s[1] && s[2] && (s[0]->type == GGML_TYPE_F32 || s[0]->type == GGML_TYPE_BF16) && f32_rows(s[1]) && s[2]->type == GGML_TYPE_I32 && f32_rows(op);
+        case B200_EXT_ADD_SINUSOID:
+            return f32_rows(s[0]) && f32_rows(op) && same_shape(s[0], op) && op->ne[2] == 1 && op->ne[3] == 1 && i32_vec(s[1]) && s[1]->ne[0] >= op->ne[1] && f32_vec(s[2]) &&
+                   s[2]->ne[0] >= (op->ne[0] + 1) / 2;
+        case B200_EXT_SHORT_CONV:
+            return f32_rows(s[0]) && f32_rows(op) && same_shape(s[0], op) && f32_vec(s[1]) && s[1]->ne[1] == op->ne[0] && s[1]->ne[0] >= 1 && s[1]->ne[0] <= 33 &&
+                   (!s[2] || (f32_vec(s[2]) && s[2]->ne[0] == op->ne[0])) && i32_vec(s[3]) && f32_rows(s[4]) && s[4]->ne[0] >= (s[1]->ne[0] - 1) * op->ne[0];
+        case B200_EXT_DELTA_RULE_SCAN:
+            for (int i = 0; i < 5; i++) if (!f32_rows(s[i])) return false;
+            return f32_vec(s[5]) && (!s[6] || f32_vec(s[6])) && i32_vec(s[7]) && f32_rows(s[8]) && f32_rows(op) && op->op_params[4] > 0 && op->op_params[4] <= 256 &&
+                   op->op_params[3] > 0 && op->op_params[2] % op->op_params[3] == 0;
+        case B200_EXT_MINGRU_SCAN:
+            return f32_rows(s[0]) && f32_rows(s[1]) && (!s[2] || f32_rows(s[2])) && (!s[3] || f32_vec(s[3])) && (!s[4] || f32_vec(s[4])) && i32_vec(s[5]) && f32_rows(s[6]) &&
+                   f32_rows(op) && s[6]->ne[0] >= op->ne[0];
         default:
             return false;
     }
@@ -109,6 +127,8 @@ static void fill_sink_attn_args(const ggml_tensor *n, b200_sink_attn_args &a) {
     a.dst = (float *)n->data; a.dst_stride = (int64_t)(n->nb[1] / 4);
     a.chunk = n->op_params[8];
     if (s[8]) { a.gate = (const float *)s[8]->data; a.gate_stride = (int64_t)(s[8]->nb[1] / 4); }
+    a.weights = n->op_params[9];
+    if (s[9]) { a.dist_bias = (const float *)s[9]->data; a.n_dist = (int32_t)s[9]->ne[1]; }
 }
 
 // the batched tensor-core form of an expert product over bf16 weights (the grouped GEMM of the quantised types)
@@ -203,9 +223,10 @@ static void run_ext(ExecCtx &x, const ggml_tensor *n) {
             if (vec && n->op_params[6]) { a.q_bias = vec; a.k_bias = vec + nq; a.v_bias = vec + nq + nk; vec += nq + nk + nv; }
             a.norm_per_head = n->op_params[7] == 2; a.rope_halves = n->op_params[8] != 0;
             if (vec && n->op_params[7]) { a.q_norm = vec; a.k_norm = vec + (a.norm_per_head ? a.dim : nq); }
-            a.pos = (const int32_t *)s[4]->data; a.freqs = (const float *)s[5]->data; a.cells = (const int32_t *)s[6]->data;
+            a.pos = (const int32_t *)s[4]->data; a.freqs = s[5] ? (const float *)s[5]->data : nullptr; a.cells = (const int32_t *)s[6]->data;
             a.k_cache = (float *)s[7]->data; a.k_cache_stride = (int64_t)(s[7]->nb[1] / 4);
             a.v_cache = (float *)s[8]->data; a.v_cache_stride = (int64_t)(s[8]->nb[1] / 4);
+            a.v_unit_rms = n->op_params[9]; a.q_temp_coef = ext_f(n, 10); a.q_temp_every = n->op_params[11];
             B200_CHECK_RC(b200_op_qkv_store(&a, x.stream));
             break;
         }
@@ -239,8 +260,9 @@ static void run_ext(ExecCtx &x, const ggml_tensor *n) {
                                                    n->op_params[5], n->op_params[2], n->op_params[3], ext_f(n, 4), n->op_params[6], n->op_params[7], s[0]->ne[1], x.stream));
             break;
         case B200_EXT_SILU_MUL: {
-            b200_tensor a = as_b200(s[0]), b = as_b200(s[1]), d = as_b200(n);
-            B200_CHECK_RC(b200_op_glu_strided(n->op_params[2], &a, &b, &d, ext_f(n, 3), ext_f(n, 4), x.stream));
+            b200_tensor a = as_b200(s[0]), b = as_b200(s[1]), d = as_b200(n), sc;
+            if (s[2]) sc = as_b200(s[2]);
+            B200_CHECK_RC(b200_op_glu_scaled(n->op_params[2], &a, &b, s[2] ? &sc : nullptr, &d, ext_f(n, 3), ext_f(n, 4), x.stream));
             break;
         }
         case B200_EXT_MOE_COMBINE:
@@ -248,6 +270,16 @@ static void run_ext(ExecCtx &x, const ggml_tensor *n) {
                 B200_CHECK_RC(b200_op_moe_combine_norm((const float *)s[0]->data, (int64_t)(s[0]->nb[1] / 4), (int64_t)(s[0]->nb[2] / 4), (const float *)s[1]->data, (int64_t)(s[1]->nb[1] / 4),
                                                        s[4] ? (const float *)s[4]->data : nullptr, ext_f(n, 3), s[2] ? (const float *)s[2]->data : nullptr,
                                                        s[2] ? (int64_t)(s[2]->nb[1] / 4) : 0, (float *)n->data, (int64_t)(n->nb[1] / 4), n->ne[0], (int32_t)s[0]->ne[1], n->ne[1], x.stream));
+                break;
+            }
+            if (s[5] || !s[0] || !s[1]) {
+                const float mult = ext_f(n, 4) == 0.0f ? 1.0f : ext_f(n, 4);
+                B200_CHECK_RC(b200_op_moe_combine_shared(s[0] ? (const float *)s[0]->data : nullptr, s[0] ? (int64_t)(s[0]->nb[1] / 4) : 0, s[0] ? (int64_t)(s[0]->nb[2] / 4) : 0,
+                                                         s[1] ? (const float *)s[1]->data : nullptr, s[1] ? (int64_t)(s[1]->nb[1] / 4) : 0, s[2] ? (const float *)s[2]->data : nullptr,
+                                                         s[2] ? (int64_t)(s[2]->nb[1] / 4) : 0, s[3] ? (const float *)s[3]->data : nullptr, s[3] ? (int64_t)(s[3]->nb[1] / 4) : 0,
+                                                         s[5] ? (const float *)s[5]->data : nullptr, s[5] ? (int64_t)(s[5]->nb[1] / 4) : 0, s[6] ? (const float *)s[6]->data : nullptr,
+                                                         s[6] ? (int64_t)(s[6]->nb[1] / 4) : 0, mult, (float *)n->data, (int64_t)(n->nb[1] / 4), n->ne[0], s[0] ? (int32_t)s[0]->ne[1] : 0,
+                                                         n->ne[1], x.stream));
                 break;
             }
             B200_CHECK_RC(b200_op_moe_combine((const float *)s[0]->data, (int64_t)(s[0]->nb[1] / 4), (int64_t)(s[0]->nb[2] / 4), (const float *)s[1]->data, (int64_t)(s[1]->nb[1] / 4),
@@ -270,6 +302,55 @@ static void run_ext(ExecCtx &x, const ggml_tensor *n) {
             }
             b200_tensor ta = as_b200(as), tb = as_b200(b), ti = as_b200(ids), td = as_b200(n);
             B200_CHECK_RC(b200_op_mul_mat_id_float(&ta, &tb, &ti, &td, x.stream));
+            break;
+        }
+        case B200_EXT_ADD_SINUSOID: {
+            b200_tensor a = as_b200(s[0]), d = as_b200(n);
+            B200_CHECK_RC(b200_op_add_sinusoid(&a, (const int32_t *)s[1]->data, (const float *)s[2]->data, &d, x.stream));
+            break;
+        }
+        case B200_EXT_SHORT_CONV: {
+            b200_short_conv_args a;
+            memset(&a, 0, sizeof(a));
+            a.x = (const float *)s[0]->data; a.x_stride = (int64_t)(s[0]->nb[1] / 4);
+            a.w = (const float *)s[1]->data; a.taps = (int32_t)s[1]->ne[0]; a.channels = (int32_t)n->ne[0];
+            a.bias = s[2] ? (const float *)s[2]->data : nullptr;
+            a.seq_info = (const int32_t *)s[3]->data; a.n_seq = (int32_t)s[3]->ne[0];
+            a.tail = (float *)s[4]->data; a.slot_stride = (int64_t)(s[4]->nb[1] / 4);
+            a.dst = (float *)n->data; a.dst_stride = (int64_t)(n->nb[1] / 4);
+            a.act = n->op_params[2]; a.n_tokens = (int32_t)n->ne[1];
+            B200_CHECK_RC(b200_op_short_conv(&a, x.stream));
+            break;
+        }
+        case B200_EXT_DELTA_RULE_SCAN: {
+            b200_delta_rule_args a;
+            memset(&a, 0, sizeof(a));
+            a.q = (const float *)s[0]->data; a.q_stride = (int64_t)(s[0]->nb[1] / 4);
+            a.k = (const float *)s[1]->data; a.k_stride = (int64_t)(s[1]->nb[1] / 4);
+            a.v = (const float *)s[2]->data; a.v_stride = (int64_t)(s[2]->nb[1] / 4);
+            a.a = (const float *)s[3]->data; a.a_stride = (int64_t)(s[3]->nb[1] / 4);
+            a.b = (const float *)s[4]->data; a.b_stride = (int64_t)(s[4]->nb[1] / 4);
+            a.a_log = (const float *)s[5]->data; a.dt_bias = s[6] ? (const float *)s[6]->data : nullptr;
+            a.seq_info = (const int32_t *)s[7]->data; a.n_seq = (int32_t)s[7]->ne[0];
+            a.state = (float *)s[8]->data; a.slot_stride = (int64_t)(s[8]->nb[1] / 4);
+            a.dst = (float *)n->data; a.dst_stride = (int64_t)(n->nb[1] / 4);
+            a.heads = n->op_params[2]; a.kv_heads = n->op_params[3]; a.dim = n->op_params[4]; a.vdim = n->op_params[5]; a.unit_qk = n->op_params[6];
+            a.unit_eps = ext_f(n, 7); a.q_scale = ext_f(n, 8);
+            B200_CHECK_RC(b200_op_delta_rule_scan(&a, x.stream));
+            break;
+        }
+        case B200_EXT_MINGRU_SCAN: {
+            b200_mingru_args a;
+            memset(&a, 0, sizeof(a));
+            a.z = (const float *)s[0]->data; a.z_stride = (int64_t)(s[0]->nb[1] / 4);
+            a.x = (const float *)s[1]->data; a.x_stride = (int64_t)(s[1]->nb[1] / 4);
+            if (s[2]) { a.g = (const float *)s[2]->data; a.g_stride = (int64_t)(s[2]->nb[1] / 4); }
+            a.z_bias = s[3] ? (const float *)s[3]->data : nullptr; a.x_bias = s[4] ? (const float *)s[4]->data : nullptr;
+            a.seq_info = (const int32_t *)s[5]->data; a.n_seq = (int32_t)s[5]->ne[0];
+            a.state = (float *)s[6]->data; a.slot_stride = (int64_t)(s[6]->nb[1] / 4);
+            a.dst = (float *)n->data; a.dst_stride = (int64_t)(n->nb[1] / 4);
+            a.width = (int32_t)n->ne[0]; a.n_tokens = (int32_t)n->ne[1];
+            B200_CHECK_RC(b200_op_mingru_scan(&a, x.stream));
             break;
         }
         default:

@@ -3,7 +3,8 @@
 //
 // Cache rows are indexed by cell, one row per token holding all kv heads; which cells a token sees follows from the (sequence,
 // position) pairs of token and cell, so a batch may mix sequences, cells may be scattered, and a sliding window with kept first
-// positions needs no mask tensor.  The sink only enters the softmax denominator.
+// positions needs no mask tensor.  The sink only enters the softmax denominator.  A table of score biases by distance (per head) may
+// join the scaled score, and the weights may be sigmoids of the scores instead of a softmax over them (nothing is normalised then).
 #include "ops_util.cuh"
 #include <cuda_bf16.h>
 
@@ -51,6 +52,8 @@ __global__ void __launch_bounds__(1024) qkv_store_kernel(const b200_qkv_store_ar
         }
     }
     const float p = (float)a.pos[t];
+    // queries grow with the logarithm of the position, in steps of q_temp_every positions
+    const float q_temp = a.q_temp_coef != 0.f ? 1.0f + a.q_temp_coef * logf((float)((a.pos[t] + 1) / max(a.q_temp_every, 1) + 1)) : 1.0f;
     const int half = a.n_dims / 2, per_head_items = half + (a.dim - a.n_dims);  // work items of a head: rotated pairs, then single values
     for (int which = 0; which < 2; which++) {
         const float *src = which ? k : q;
@@ -65,7 +68,7 @@ __global__ void __launch_bounds__(1024) qkv_store_kernel(const b200_qkv_store_ar
                 const int e = hh * a.dim + a.n_dims + (j - half);
                 float x = src[e] + (bias ? bias[e] : 0.f);
                 if (nw) x = x * sc * nw[e - wb];
-                dst[e] = x;
+                dst[e] = which ? x : x * q_temp;
                 continue;
             }
             const int e0 = hh * a.dim + (a.rope_halves ? j : 2 * j), e1 = a.rope_halves ? e0 + half : e0 + 1;
@@ -73,9 +76,21 @@ __global__ void __launch_bounds__(1024) qkv_store_kernel(const b200_qkv_store_ar
             if (nw) { u = u * sc * nw[e0 - wb]; w = w * sc * nw[e1 - wb]; }
             float sn, cs;
             sincosf(p * a.freqs[j], &sn, &cs);
-            dst[e0] = u * cs - w * sn;
-            dst[e1] = w * cs + u * sn;
+            const float tq = which ? 1.0f : q_temp;
+            dst[e0] = (u * cs - w * sn) * tq;
+            dst[e1] = (w * cs + u * sn) * tq;
         }
+    }
+    if (a.v_unit_rms) {  // a warp per head of v: statistics, then the scaled row
+        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
+        for (int hh = warp; hh < a.n_head_kv; hh += n_warps) {
+            const int e0 = hh * a.vdim;
+            float ss = 0.f;
+            for (int i = lane; i < a.vdim; i += 32) { const float x = v[e0 + i] + (a.v_bias ? a.v_bias[e0 + i] : 0.f); ss += x * x; }
+            const float sc = 1.0f / sqrtf(warp_sum(ss) / (float)a.vdim + a.eps);
+            for (int i = lane; i < a.vdim; i += 32) vc[e0 + i] = (v[e0 + i] + (a.v_bias ? a.v_bias[e0 + i] : 0.f)) * sc;
+        }
+        return;
     }
     for (int i = threadIdx.x; i < nv; i += blockDim.x) vc[i] = v[i] + (a.v_bias ? a.v_bias[i] : 0.f);
 }
@@ -85,6 +100,11 @@ __device__ __forceinline__ bool sa_visible(int cell_seq, int cell_pos, int seq, 
     return cell_seq == seq && cell_pos <= pos && cell_pos >= lo && (window <= 0 || pos - cell_pos < window || cell_pos < keep_first);
 }
 __device__ __forceinline__ int sa_chunk_start(int pos, int chunk) { return chunk > 0 ? pos - pos % chunk : 0; }
+// the bias of a key `dist` positions behind the query (0 without a table)
+__device__ __forceinline__ float sa_dist_bias(const b200_sink_attn_args &a, int dist, int h) {
+    return a.dist_bias ? a.dist_bias[(int64_t)min(dist, a.n_dist - 1) * a.n_head + h] : 0.f;
+}
+__device__ __forceinline__ float sa_sigmoid(float x) { return 1.0f / (1.0f + expf(-x)); }
 __device__ __forceinline__ float sa_head_gate(const b200_sink_attn_args &a, int64_t t, int h) {
     return a.gate ? 1.0f / (1.0f + expf(-a.gate[t * a.gate_stride + h])) : 1.0f;
 }
@@ -112,12 +132,19 @@ __global__ void __launch_bounds__(WARPS * 32) sink_attn_kernel(const b200_sink_a
 #pragma unroll
     for (int i = 0; i < NV; i++) acc[i] = 0.f;
     const int seq = a.tok_seq[t], pos = a.tok_pos[t], lo = sa_chunk_start(pos, a.chunk);
-    float m = -INFINITY, l = 0.f;
+    const bool sig = a.weights == B200_ATTN_SIGMOID;
+    float m = sig ? 0.f : -INFINITY, l = 0.f;  // sigmoid weights: no maximum, no sum; the warps' accumulators simply add up
     const int per_split = ((a.n_kv + n_split - 1) / n_split + 31) & ~31;
     const int c_begin = (int)blockIdx.z * per_split, c_end = min(a.n_kv, c_begin + per_split);
     for (int cb = c_begin + warp * 32; cb < c_end; cb += WARPS * 32) {
         bool mine = false;
-        if (cb + lane < c_end) mine = sa_visible(a.cell_seq[cb + lane], a.cell_pos[cb + lane], seq, pos, a.window, a.keep_first, lo);
+        int my_dist = 0;
+        if (cb + lane < c_end) {
+            const int cp = a.cell_pos[cb + lane];
+            mine = sa_visible(a.cell_seq[cb + lane], cp, seq, pos, a.window, a.keep_first, lo);
+            my_dist = pos - cp;
+        }
+        const float my_bias = mine ? sa_dist_bias(a, my_dist, h) : 0.f;  // lane j holds the bias of cell cb + j
         unsigned rest = __ballot_sync(0xffffffffu, mine);
         while (rest) {
             bool vis[SA_UNROLL];  // warp-uniform
@@ -147,10 +174,16 @@ __global__ void __launch_bounds__(WARPS * 32) sink_attn_kernel(const b200_sink_a
                 for (int i = 0; i < ND; i++) s[u] += q[i] * kv[u][i];
             }
 #pragma unroll
-            for (int u = 0; u < SA_UNROLL; u++) if (vis[u]) s[u] = warp_sum(s[u]);
+            for (int u = 0; u < SA_UNROLL; u++) if (vis[u]) s[u] = warp_sum(s[u]) + __shfl_sync(0xffffffffu, my_bias, cu[u] - cb);
 #pragma unroll
             for (int u = 0; u < SA_UNROLL; u++) {
                 if (!vis[u]) continue;
+                if (sig) {
+                    const float p = sa_sigmoid(s[u]);
+#pragma unroll
+                    for (int i = 0; i < NV; i++) acc[i] += p * vv[u][i];
+                    continue;
+                }
                 const float mn = fmaxf(m, s[u]);
                 const float corr = expf(m - mn), p = expf(s[u] - mn);  // m = -inf at the first cell: corr = 0
                 l = l * corr + p;
@@ -165,7 +198,7 @@ __global__ void __launch_bounds__(WARPS * 32) sink_attn_kernel(const b200_sink_a
     for (int i = 0; i < NV; i++) { const int j = lane + 32 * i; if (j < V) sacc[j] = acc[i]; }
     if (lane == 0) { sm[warp] = m; sl[warp] = l; }
     __syncthreads();
-    const float sink = (a.sink && n_split == 1) ? a.sink[h] : -INFINITY;  // split: the merge adds the sink
+    const float sink = (a.sink && n_split == 1 && !sig) ? a.sink[h] : -INFINITY;  // split: the merge adds the sink
     float M = sink;
     for (int w = 0; w < WARPS; w++) M = fmaxf(M, sm[w]);
     float L = sink != -INFINITY ? expf(sink - M) : 0.f;
@@ -183,7 +216,8 @@ __global__ void __launch_bounds__(WARPS * 32) sink_attn_kernel(const b200_sink_a
         }
         return;
     }
-    const float inv = (L > 0.f ? 1.0f / L : 0.f) * sa_head_gate(a, t, h);
+    // sigmoid weights: every warp's maximum is 0, so M = 0, the warps' merge weights are 1 and nothing is divided
+    const float inv = (sig ? 1.0f : (L > 0.f ? 1.0f / L : 0.f)) * sa_head_gate(a, t, h);
     float *out = a.dst + (int64_t)t * a.dst_stride + (int64_t)h * V;
     for (int j = threadIdx.x; j < V; j += blockDim.x) {
         float o = 0.f;
@@ -198,12 +232,13 @@ __global__ void __launch_bounds__(128) sink_attn_merge_kernel(const b200_sink_at
     const int V = a.vdim, h = (int)(pair % a.n_head);
     const int64_t t = pair / a.n_head;
     const float *pp = part + pair * n_split * (V + 2);
-    const float sink = a.sink ? a.sink[h] : -INFINITY;
+    const bool sig = a.weights == B200_ATTN_SIGMOID;  // every stretch reports the maximum 0: the stretches add up
+    const float sink = (a.sink && !sig) ? a.sink[h] : -INFINITY;
     float M = sink;
     for (int z = 0; z < n_split; z++) M = fmaxf(M, pp[(int64_t)z * (V + 2)]);
-    float L = a.sink ? expf(sink - M) : 0.f;
+    float L = sink != -INFINITY ? expf(sink - M) : 0.f;
     for (int z = 0; z < n_split; z++) { const float mz = pp[(int64_t)z * (V + 2)]; if (mz != -INFINITY) L += pp[(int64_t)z * (V + 2) + 1] * expf(mz - M); }
-    const float inv = (L > 0.f ? 1.0f / L : 0.f) * sa_head_gate(a, t, h);
+    const float inv = (sig ? 1.0f : (L > 0.f ? 1.0f / L : 0.f)) * sa_head_gate(a, t, h);
     float *out = a.dst + t * a.dst_stride + (int64_t)h * V;
     for (int j = threadIdx.x; j < V; j += blockDim.x) {
         float o = 0.f;
@@ -341,6 +376,7 @@ __global__ void __launch_bounds__(GM_WARPS * 32) sink_attn_mma_kernel(const b200
 #pragma unroll
     for (int j = 0; j < 2 * VS; j++) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;  // rows g and g + 8; l: this lane's share of the row sum
+    const bool sig = a.weights == B200_ATTN_SIGMOID;
 
     for (int c0 = 0; c0 < a.n_kv; c0 += GM_CELLS) {
         // does any of the warp's tokens see any of the tile's cells?  lane = cell
@@ -381,10 +417,29 @@ __global__ void __launch_bounds__(GM_WARPS * 32) sink_attn_mma_kernel(const b200
             for (int e = 0; e < 2; e++) {
                 const int c = j * 8 + 2 * t4 + e;
                 const int xs = cseq[c], xp = cpos[c];
-                s[j][e] = sa_visible(xs, xp, rs0, rp0, a.window, a.keep_first, rl0) ? s[j][e] * a.scale : -INFINITY;
-                s[j][2 + e] = sa_visible(xs, xp, rs1, rp1, a.window, a.keep_first, rl1) ? s[j][2 + e] * a.scale : -INFINITY;
+                s[j][e] = sa_visible(xs, xp, rs0, rp0, a.window, a.keep_first, rl0) ? s[j][e] * a.scale + sa_dist_bias(a, rp0 - xp, h) : -INFINITY;
+                s[j][2 + e] = sa_visible(xs, xp, rs1, rp1, a.window, a.keep_first, rl1) ? s[j][2 + e] * a.scale + sa_dist_bias(a, rp1 - xp, h) : -INFINITY;
                 mx0 = fmaxf(mx0, s[j][e]); mx1 = fmaxf(mx1, s[j][2 + e]);
             }
+        }
+        if (sig) {  // every visible key's weight is the sigmoid of its own score (0 for the others: the sigmoid of -inf); nothing is rescaled
+            unsigned pa[GM_CELLS / 16][4];
+#pragma unroll
+            for (int j = 0; j < GM_CELLS / 8; j++) {
+                pa[j >> 1][(j & 1) * 2] = gm_pack_bf2(sa_sigmoid(s[j][0]), sa_sigmoid(s[j][1]));
+                pa[j >> 1][(j & 1) * 2 + 1] = gm_pack_bf2(sa_sigmoid(s[j][2]), sa_sigmoid(s[j][3]));
+            }
+#pragma unroll
+            for (int kk = 0; kk < GM_CELLS / 16; kk++) {
+#pragma unroll
+                for (int j = 0; j < VS; j++) {
+                    unsigned b0, b1, b2, b3;
+                    gm_ldsm4_t(vs_u + kk * 16 * VSTRIDE + v_off + j * 32, b0, b1, b2, b3);
+                    gm_mma_bf16(o[2 * j], pa[kk], b0, b1);
+                    gm_mma_bf16(o[2 * j + 1], pa[kk], b2, b3);
+                }
+            }
+            continue;
         }
         mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
         mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
@@ -422,7 +477,9 @@ __global__ void __launch_bounds__(GM_WARPS * 32) sink_attn_mma_kernel(const b200
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
     const float sink = a.sink ? a.sink[h] : -INFINITY;
     float w[2];
-    {
+    if (sig) {
+        w[0] = w[1] = 1.0f;
+    } else {
         const float M0 = fmaxf(m0, sink), M1 = fmaxf(m1, sink);
         const float f0 = m0 == -INFINITY ? 0.f : expf(m0 - M0), f1 = m1 == -INFINITY ? 0.f : expf(m1 - M1);
         const float d0 = l0 * f0 + (a.sink ? expf(sink - M0) : 0.f), d1 = l1 * f1 + (a.sink ? expf(sink - M1) : 0.f);
@@ -610,6 +667,7 @@ extern "C" int b200_op_sink_attn_ws(const b200_sink_attn_args *a, void *workspac
     OPX_REQUIRE(a && a->q && a->k_cache && a->v_cache && a->cell_seq && a->cell_pos && a->tok_seq && a->tok_pos && a->dst, B200_ERR_INVALID, "b200_op_sink_attn: NULL argument");
     OPX_REQUIRE(a->n_head > 0 && a->n_head <= 65535 && a->n_head_kv > 0 && a->n_head % a->n_head_kv == 0 && a->dim > 0 && a->dim <= 256 && a->vdim > 0 && a->vdim <= 256 &&
                 a->n_tokens >= 0 && a->n_kv >= 0 && a->window >= 0 && a->keep_first >= 0 && a->chunk >= 0, B200_ERR_UNSUPPORTED, "b200_op_sink_attn: head sizes up to 256, heads up to 65535");
+    OPX_REQUIRE((a->weights == B200_ATTN_SOFTMAX || a->weights == B200_ATTN_SIGMOID) && (!a->dist_bias || a->n_dist > 0), B200_ERR_INVALID, "b200_op_sink_attn: weight kind / distance table");
     if (a->n_tokens == 0) return B200_OK;
     const cudaStream_t st = (cudaStream_t)stream;
     if (sink_attn_mma_ok(a)) return launch_sink_attn_mma(a, st);

@@ -7,7 +7,7 @@
 #include "host_model.h"
 
 const Arch *b200::host::find_arch(int32_t id) {
-    return id == B200_ARCH_GENESUN ? genesun_arch() : id == B200_ARCH_GALIRAX ? galirax_arch() : id == B200_ARCH_ZEVOPEL ? zevopel_arch() : nullptr;
+    return id == B200_ARCH_GENESUN ? genesun_arch() : id == B200_ARCH_GALIRAX ? galirax_arch() : id == B200_ARCH_ZEVOPEL ? zevopel_arch() : id == B200_ARCH_MEDODRA ? medodra_arch() : nullptr;
 }
 
 extern "C" int b200_llama_new(const b200_llama_params *p, b200_llama **out) {

@@ -263,6 +263,7 @@ const Arch *find_arch(int32_t id);
 const Arch *genesun_arch();
 const Arch *galirax_arch();
 const Arch *zevopel_arch();
+const Arch *medodra_arch();
 
 }  // namespace host
 }  // namespace b200

@@ -188,12 +188,16 @@ __device__ __forceinline__ float glu_value(float x, float u, float limit, float 
     return x / (1.0f + expf(-x)) * u;
 }
 template <int KIND>
-__global__ void glu_strided_kernel(TD a, TD b, TD dst, int64_t n, float limit, float alpha) {
+__global__ void glu_strided_kernel(TD a, TD b, TD sc, bool has_scale, TD dst, int64_t n, float limit, float alpha) {
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     const int64_t i0 = i % dst.ne[0], i1 = (i / dst.ne[0]) % dst.ne[1], i2 = (i / (dst.ne[0] * dst.ne[1])) % dst.ne[2], i3 = i / (dst.ne[0] * dst.ne[1] * dst.ne[2]);
-    const float x = *(const float *)(a.data + i0 * a.nb[0] + i1 * a.nb[1] + i2 * a.nb[2] + i3 * a.nb[3]);
-    const float u = *(const float *)(b.data + i0 * b.nb[0] + i1 * b.nb[1] + i2 * b.nb[2] + i3 * b.nb[3]);
+    float x = *(const float *)(a.data + i0 * a.nb[0] + i1 * a.nb[1] + i2 * a.nb[2] + i3 * a.nb[3]);
+    float u = *(const float *)(b.data + i0 * b.nb[0] + i1 * b.nb[1] + i2 * b.nb[2] + i3 * b.nb[3]);
+    if (has_scale) {  // the two products are linear in their input: a factor on the input is a factor on both
+        const float f = *(const float *)(sc.data + i1 * sc.nb[0] + i2 * sc.nb[1]);
+        x *= f; u *= f;
+    }
     *(float *)(dst.data + i0 * dst.nb[0] + i1 * dst.nb[1] + i2 * dst.nb[2] + i3 * dst.nb[3]) = glu_value<KIND>(x, u, limit, alpha);
 }
 
@@ -206,6 +210,24 @@ __global__ void moe_combine_kernel(const float *__restrict__ y, int64_t y_s_slot
     float s = 0.f;
     for (int k = 0; k < n_used; k++) s += w[t * w_s_tok + k] * y[t * y_s_tok + k * y_s_slot + i];
     if (add1) s += add1[t * add1_stride + i];  // the two sublayers first, then the residual stream
+    if (add0) s += add0[t * add0_stride + i];
+    dst[t * dst_stride + i] = s;
+}
+
+// The chosen experts' results (weights optional), a shared expert's result times the sigmoid of its per-token gate logit, the other
+// sublayer's result; their sum times the residual multiplier joins the stream.
+__global__ void moe_combine_shared_kernel(const float *__restrict__ y, int64_t y_s_slot, int64_t y_s_tok, const float *__restrict__ w, int64_t w_s_tok,
+                                          const float *__restrict__ add0, int64_t add0_stride, const float *__restrict__ add1, int64_t add1_stride,
+                                          const float *__restrict__ shared, int64_t shared_stride, const float *__restrict__ gate, int64_t gate_stride, float mult,
+                                          float *__restrict__ dst, int64_t dst_stride, int64_t n, int n_used, int64_t total) {
+    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const int64_t t = idx / n, i = idx - t * n;
+    float s = 0.f;
+    for (int k = 0; k < n_used; k++) s += (w ? w[t * w_s_tok + k] : 1.0f) * y[t * y_s_tok + k * y_s_slot + i];
+    if (shared) s += shared[t * shared_stride + i] * (gate ? sigmoidf_(gate[t * gate_stride]) : 1.0f);
+    if (add1) s += add1[t * add1_stride + i];
+    s *= mult;
     if (add0) s += add0[t * add0_stride + i];
     dst[t * dst_stride + i] = s;
 }
@@ -310,16 +332,24 @@ extern "C" int b200_op_silu_mul_strided(const b200_tensor *a, const b200_tensor 
 }
 
 extern "C" int b200_op_glu_strided(int kind, const b200_tensor *a, const b200_tensor *b, const b200_tensor *dst, float limit, float alpha, b200_stream_t stream) {
+    return b200_op_glu_scaled(kind, a, b, nullptr, dst, limit, alpha, stream);
+}
+
+extern "C" int b200_op_glu_scaled(int kind, const b200_tensor *a, const b200_tensor *b, const b200_tensor *scale, const b200_tensor *dst, float limit, float alpha,
+                                  b200_stream_t stream) {
     OPX_REQUIRE(a && b && dst && a->data && b->data && dst->data, B200_ERR_INVALID, "b200_op_glu_strided: NULL argument");
+    OPX_REQUIRE(!scale || (scale->data && scale->type == B200_TYPE_F32 && scale->ne[0] == dst->ne[1] && scale->ne[1] == dst->ne[2] && dst->ne[3] == 1), B200_ERR_INVALID,
+                "b200_op_glu_scaled: the scale is one f32 value per (i1, i2)");
+    const TD tsc = scale ? td(scale) : td(dst);
     OPX_REQUIRE(a->type == B200_TYPE_F32 && b->type == B200_TYPE_F32 && dst->type == B200_TYPE_F32 && same_shape(a, dst) && same_shape(b, dst), B200_ERR_UNSUPPORTED,
                 "b200_op_glu_strided: f32 tensors of one shape only");
     OPX_REQUIRE(kind == B200_GLU_SILU || kind == B200_GLU_GELU_TANH || kind == B200_GLU_SWISH_CLAMPED, B200_ERR_INVALID, "b200_op_glu_strided: unknown kind %d", kind);
     const int64_t n = nelements(dst);
     if (n == 0) return B200_OK;
     const cudaStream_t st = (cudaStream_t)stream;
-    if (kind == B200_GLU_GELU_TANH) glu_strided_kernel<B200_GLU_GELU_TANH><<<grid1d(n, 256), 256, 0, st>>>(td(a), td(b), td(dst), n, limit, alpha);
-    else if (kind == B200_GLU_SWISH_CLAMPED) glu_strided_kernel<B200_GLU_SWISH_CLAMPED><<<grid1d(n, 256), 256, 0, st>>>(td(a), td(b), td(dst), n, limit, alpha);
-    else glu_strided_kernel<B200_GLU_SILU><<<grid1d(n, 256), 256, 0, st>>>(td(a), td(b), td(dst), n, limit, alpha);
+    if (kind == B200_GLU_GELU_TANH) glu_strided_kernel<B200_GLU_GELU_TANH><<<grid1d(n, 256), 256, 0, st>>>(td(a), td(b), tsc, scale != nullptr, td(dst), n, limit, alpha);
+    else if (kind == B200_GLU_SWISH_CLAMPED) glu_strided_kernel<B200_GLU_SWISH_CLAMPED><<<grid1d(n, 256), 256, 0, st>>>(td(a), td(b), tsc, scale != nullptr, td(dst), n, limit, alpha);
+    else glu_strided_kernel<B200_GLU_SILU><<<grid1d(n, 256), 256, 0, st>>>(td(a), td(b), tsc, scale != nullptr, td(dst), n, limit, alpha);
     B200_CUDA_TRY(cudaGetLastError());
     return B200_OK;
 }
@@ -344,6 +374,18 @@ extern "C" int b200_op_moe_combine(const float *y, int64_t y_s_slot, int64_t y_s
     const int64_t total = n * n_tok;
     if (total == 0) return B200_OK;
     moe_combine_kernel<<<grid1d(total, 256), 256, 0, (cudaStream_t)stream>>>(y, y_s_slot, y_s_tok, w, w_s_tok, add0, add0_stride, add1, add1_stride, dst, dst_stride, n, n_used, total);
+    B200_CUDA_TRY(cudaGetLastError());
+    return B200_OK;
+}
+
+extern "C" int b200_op_moe_combine_shared(const float *y, int64_t y_s_slot, int64_t y_s_tok, const float *w, int64_t w_s_tok, const float *add0, int64_t add0_stride,
+                                          const float *add1, int64_t add1_stride, const float *shared, int64_t shared_stride, const float *gate, int64_t gate_stride,
+                                          float mult, float *dst, int64_t dst_stride, int64_t n, int32_t n_used, int64_t n_tok, b200_stream_t stream) {
+    OPX_REQUIRE(dst && n >= 0 && n_used >= 0 && n_tok >= 0 && (y || n_used == 0), B200_ERR_INVALID, "b200_op_moe_combine_shared: bad argument");
+    const int64_t total = n * n_tok;
+    if (total == 0) return B200_OK;
+    moe_combine_shared_kernel<<<grid1d(total, 256), 256, 0, (cudaStream_t)stream>>>(y, y_s_slot, y_s_tok, w, w_s_tok, add0, add0_stride, add1, add1_stride, shared, shared_stride,
+                                                                                   gate, gate_stride, mult, dst, dst_stride, n, n_used, total);
     B200_CUDA_TRY(cudaGetLastError());
     return B200_OK;
 }

@@ -10,7 +10,7 @@ using namespace opx;
 // ------------------------------------------------------------------------------------------------ norm (+ gate, + residual)
 template <int KIND, bool GATE>
 __global__ void norm_kernel(TD x, const float *__restrict__ w, int64_t w_period, const float *__restrict__ bias, TD gate, const float *__restrict__ gate_bias,
-                            bool gate_out, TD res, bool has_res, TD dst, float eps) {
+                            int gate_out, TD res, bool has_res, TD dst, float eps) {
     __shared__ float sh[32];
     extern __shared__ float rowbuf[];  // the gated row (GATE only)
     const int64_t r = blockIdx.x;
@@ -45,7 +45,7 @@ __global__ void norm_kernel(TD x, const float *__restrict__ w, int64_t w_period,
         float v = (src[i] - mean) * scale;
         if (wr) v *= wr[i];
         if (bias) v += bias[i];
-        if (GATE && gate_out) v *= sigmoidf_(gr[i] + (gate_bias ? gate_bias[i] : 0.f));
+        if (GATE && gate_out) { const float z = gr[i] + (gate_bias ? gate_bias[i] : 0.f); v *= gate_out == 2 ? z * sigmoidf_(z) : sigmoidf_(z); }
         if (rr) v += rr[i];
         yr[i] = v;
     }
@@ -77,7 +77,7 @@ __global__ void polynorm_kernel(TD x, const float *__restrict__ coef, TD dst, fl
 // reduction, so a row costs one memory latency for the statistics and one for the weight / residual, whatever its length.
 template <int KIND, bool GATE, int VPT>
 __global__ void __launch_bounds__(1024) norm_reg_kernel(TD x, const float *__restrict__ w, int64_t w_period, const float *__restrict__ bias, TD gate,
-                                                        const float *__restrict__ gate_bias, bool gate_out, TD res, bool has_res, TD dst, float eps) {
+                                                        const float *__restrict__ gate_bias, int gate_out, TD res, bool has_res, TD dst, float eps) {
     __shared__ float sh[32];
     const int64_t r = blockIdx.x;
     const float *xr = (const float *)row_ptr(x, r);
@@ -118,7 +118,7 @@ __global__ void __launch_bounds__(1024) norm_reg_kernel(TD x, const float *__res
         if (i < n) {
             float y = (v[k] - mean) * scale * wv[k];
             if (bias) y += bias[i];
-            if (GATE && gate_out) y *= sigmoidf_(g[k]);
+            if (GATE && gate_out) y *= gate_out == 2 ? g[k] * sigmoidf_(g[k]) : sigmoidf_(g[k]);
             yr[i] = y + rv[k];
         }
     }
@@ -197,10 +197,34 @@ __global__ void sigmoid_mul_kernel(TD a, TD b, TD dst, int64_t n) {
 
 static unsigned grid1d(int64_t n, int block) { return (unsigned)((n + block - 1) / block); }
 
+// position vector of sines and cosines added to every row: a thread per pair (2i, 2i + 1), the angle pos * f_i in f32
+__global__ void add_sinusoid_kernel(TD x, const int32_t *__restrict__ pos, const float *__restrict__ freqs, TD dst, int64_t pairs, int64_t total) {
+    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const int64_t t = idx / pairs, i = idx - t * pairs;
+    const float *xr = (const float *)(x.data + t * x.nb[1]);
+    float *yr = (float *)(dst.data + t * dst.nb[1]);
+    float sn, cs;
+    sincosf((float)pos[t] * freqs[i], &sn, &cs);
+    yr[2 * i] = xr[2 * i] + sn;
+    if (2 * i + 1 < x.ne[0]) yr[2 * i + 1] = xr[2 * i + 1] + cs;
+}
+
 }  // namespace b200
 
 using namespace b200;
 using namespace b200::opx;
+
+extern "C" int b200_op_add_sinusoid(const b200_tensor *x, const int32_t *pos, const float *freqs, const b200_tensor *dst, b200_stream_t stream) {
+    OPX_REQUIRE(x && dst && pos && freqs && x->data && dst->data, B200_ERR_INVALID, "b200_op_add_sinusoid: NULL argument");
+    OPX_REQUIRE(x->type == B200_TYPE_F32 && dst->type == B200_TYPE_F32 && x->nb[0] == 4 && dst->nb[0] == 4 && same_shape(x, dst) && x->ne[2] == 1 && x->ne[3] == 1, B200_ERR_UNSUPPORTED,
+                "b200_op_add_sinusoid: f32 [n, tokens] rows only");
+    const int64_t pairs = (x->ne[0] + 1) / 2, total = pairs * x->ne[1];
+    if (total == 0) return B200_OK;
+    add_sinusoid_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(td(x), pos, freqs, td(dst), pairs, total);
+    B200_CUDA_TRY(cudaGetLastError());
+    return B200_OK;
+}
 
 extern "C" int b200_op_norm(const b200_tensor *x, const float *w, int64_t w_period, const b200_tensor *gate, const float *gate_bias, const b200_tensor *res,
                             const b200_tensor *dst, float eps, int kind, b200_stream_t stream) {
@@ -209,7 +233,8 @@ extern "C" int b200_op_norm(const b200_tensor *x, const float *w, int64_t w_peri
 
 extern "C" int b200_op_norm_affine(const b200_tensor *x, const float *w, int64_t w_period, const float *bias, const b200_tensor *gate, const float *gate_bias,
                                    int gate_on_output, const b200_tensor *res, const b200_tensor *dst, float eps, int kind, b200_stream_t stream) {
-    const bool gate_out = gate && gate_on_output != 0;
+    const int gate_out = gate ? gate_on_output : 0;  // 0: in front of the norm; 1: sigmoid on the output; 2: silu on the output
+    OPX_REQUIRE(gate_out >= 0 && gate_out <= 2, B200_ERR_INVALID, "b200_op_norm: unknown gate placement %d", gate_on_output);
     OPX_REQUIRE(x && dst && x->data && dst->data, B200_ERR_INVALID, "b200_op_norm: NULL argument");
     OPX_REQUIRE(x->type == B200_TYPE_F32 && dst->type == B200_TYPE_F32 && x->nb[0] == 4 && dst->nb[0] == 4 && same_shape(x, dst), B200_ERR_UNSUPPORTED,
                 "b200_op_norm: f32 rows of one shape only");

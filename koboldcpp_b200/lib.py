@@ -87,7 +87,8 @@ class QkvStoreArgs(C.Structure):
                 ("q_bias", C.c_void_p), ("k_bias", C.c_void_p), ("v_bias", C.c_void_p), ("q_norm", C.c_void_p), ("k_norm", C.c_void_p),
                 ("pos", C.c_void_p), ("cells", C.c_void_p), ("freqs", C.c_void_p), ("k_cache", C.c_void_p), ("k_cache_stride", C.c_int64),
                 ("v_cache", C.c_void_p), ("v_cache_stride", C.c_int64), ("n_head", C.c_int32), ("n_head_kv", C.c_int32), ("dim", C.c_int32),
-                ("vdim", C.c_int32), ("n_dims", C.c_int32), ("n_tokens", C.c_int32), ("eps", C.c_float), ("norm_per_head", C.c_int32), ("rope_halves", C.c_int32)]
+                ("vdim", C.c_int32), ("n_dims", C.c_int32), ("n_tokens", C.c_int32), ("eps", C.c_float), ("norm_per_head", C.c_int32), ("rope_halves", C.c_int32),
+                ("v_unit_rms", C.c_int32), ("q_temp_coef", C.c_float), ("q_temp_every", C.c_int32)]
 
 
 class SinkAttnArgs(C.Structure):
@@ -96,7 +97,8 @@ class SinkAttnArgs(C.Structure):
                 ("v_cache_stride", C.c_int64), ("cell_seq", C.c_void_p), ("cell_pos", C.c_void_p), ("tok_seq", C.c_void_p), ("tok_pos", C.c_void_p),
                 ("sink", C.c_void_p), ("dst", C.c_void_p), ("dst_stride", C.c_int64), ("n_head", C.c_int32), ("n_head_kv", C.c_int32), ("dim", C.c_int32),
                 ("vdim", C.c_int32), ("n_tokens", C.c_int32), ("n_kv", C.c_int32), ("window", C.c_int32), ("keep_first", C.c_int32), ("scale", C.c_float),
-                ("bf16_products", C.c_int32), ("chunk", C.c_int32), ("gate", C.c_void_p), ("gate_stride", C.c_int64)]
+                ("bf16_products", C.c_int32), ("chunk", C.c_int32), ("gate", C.c_void_p), ("gate_stride", C.c_int64),
+                ("weights", C.c_int32), ("dist_bias", C.c_void_p), ("n_dist", C.c_int32)]
 
 
 class LinearAttnArgs(C.Structure):
@@ -104,6 +106,29 @@ class LinearAttnArgs(C.Structure):
     _fields_ = [("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("q_stride", C.c_int64), ("k_stride", C.c_int64), ("v_stride", C.c_int64),
                 ("decay", C.c_void_p), ("seq_info", C.c_void_p), ("n_seq", C.c_int32), ("state", C.c_void_p), ("slot_stride", C.c_int64),
                 ("dst", C.c_void_p), ("dst_stride", C.c_int64), ("heads", C.c_int32), ("dim", C.c_int32), ("vdim", C.c_int32), ("act", C.c_int32)]
+
+
+class ShortConvArgs(C.Structure):
+    """b200_short_conv_args (include/b200_ggml_ops.h); strides in floats."""
+    _fields_ = [("x", C.c_void_p), ("x_stride", C.c_int64), ("bias", C.c_void_p), ("w", C.c_void_p), ("seq_info", C.c_void_p), ("n_seq", C.c_int32),
+                ("tail", C.c_void_p), ("slot_stride", C.c_int64), ("dst", C.c_void_p), ("dst_stride", C.c_int64), ("channels", C.c_int32), ("taps", C.c_int32),
+                ("act", C.c_int32), ("n_tokens", C.c_int32)]
+
+
+class DeltaRuleArgs(C.Structure):
+    """b200_delta_rule_args (include/b200_ggml_ops.h); strides in floats."""
+    _fields_ = [("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("q_stride", C.c_int64), ("k_stride", C.c_int64), ("v_stride", C.c_int64),
+                ("a", C.c_void_p), ("b", C.c_void_p), ("a_stride", C.c_int64), ("b_stride", C.c_int64), ("a_log", C.c_void_p), ("dt_bias", C.c_void_p),
+                ("seq_info", C.c_void_p), ("n_seq", C.c_int32), ("state", C.c_void_p), ("slot_stride", C.c_int64), ("dst", C.c_void_p), ("dst_stride", C.c_int64),
+                ("heads", C.c_int32), ("kv_heads", C.c_int32), ("dim", C.c_int32), ("vdim", C.c_int32), ("unit_qk", C.c_int32), ("unit_eps", C.c_float),
+                ("q_scale", C.c_float)]
+
+
+class MinGruArgs(C.Structure):
+    """b200_mingru_args (include/b200_ggml_ops.h); strides in floats."""
+    _fields_ = [("z", C.c_void_p), ("x", C.c_void_p), ("g", C.c_void_p), ("z_stride", C.c_int64), ("x_stride", C.c_int64), ("g_stride", C.c_int64),
+                ("z_bias", C.c_void_p), ("x_bias", C.c_void_p), ("seq_info", C.c_void_p), ("n_seq", C.c_int32), ("state", C.c_void_p), ("slot_stride", C.c_int64),
+                ("dst", C.c_void_p), ("dst_stride", C.c_int64), ("width", C.c_int32), ("n_tokens", C.c_int32)]
 
 
 _SIGS = {
@@ -194,6 +219,13 @@ _OPS_SIGS = {
     "b200_op_moe_combine_norm": (C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_float, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64,
                                            C.c_int64, C.c_int32, C.c_int64, C.c_void_p]),
     "b200_op_mul_mat_id_float": (C.c_int, [C.POINTER(Tensor), C.POINTER(Tensor), C.POINTER(Tensor), C.POINTER(Tensor), C.c_void_p]),
+    "b200_op_glu_scaled": (C.c_int, [C.c_int, C.POINTER(Tensor), C.POINTER(Tensor), C.POINTER(Tensor), C.POINTER(Tensor), C.c_float, C.c_float, C.c_void_p]),
+    "b200_op_moe_combine_shared": (C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64,
+                                             C.c_void_p, C.c_int64, C.c_float, C.c_void_p, C.c_int64, C.c_int64, C.c_int32, C.c_int64, C.c_void_p]),
+    "b200_op_add_sinusoid": (C.c_int, [C.POINTER(Tensor), C.c_void_p, C.c_void_p, C.POINTER(Tensor), C.c_void_p]),
+    "b200_op_short_conv": (C.c_int, [C.POINTER(ShortConvArgs), C.c_void_p]),
+    "b200_op_delta_rule_scan": (C.c_int, [C.POINTER(DeltaRuleArgs), C.c_void_p]),
+    "b200_op_mingru_scan": (C.c_int, [C.POINTER(MinGruArgs), C.c_void_p]),
 }
 
 _lib = None

@@ -33,7 +33,9 @@ class LayerParams(C.Structure):
                 ("band_low", C.c_float), ("band_high", C.c_float),
                 ("n_expert", C.c_int32), ("n_expert_used", C.c_int32), ("n_group", C.c_int32), ("n_group_used", C.c_int32), ("router_scale", C.c_float),
                 ("chunk", C.c_int32), ("qk_norm_per_head", C.c_int32), ("rope_halves", C.c_int32), ("head_gate", C.c_int32),
-                ("glu_kind", C.c_int32), ("glu_limit", C.c_float), ("glu_alpha", C.c_float), ("router_score", C.c_int32), ("router_keep_scores", C.c_int32)]
+                ("glu_kind", C.c_int32), ("glu_limit", C.c_float), ("glu_alpha", C.c_float), ("router_score", C.c_int32), ("router_keep_scores", C.c_int32),
+                ("conv_taps", C.c_int32), ("q_temp_coef", C.c_float), ("q_temp_every", C.c_int32), ("dist_bias_max", C.c_int32), ("side_width", C.c_int32),
+                ("router_scale_input", C.c_int32), ("shared_ff", C.c_int32), ("loop_input", C.c_int32)]
 
 
 _SIGS = {

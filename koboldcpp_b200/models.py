@@ -4,13 +4,14 @@ from __future__ import annotations
 import json
 from pathlib import Path
 
-from . import galirax, genesun, zevopel
+from . import galirax, genesun, medodra, zevopel
 from .lib import B200Error
 
 ARCHITECTURES = {
     "Genesun": genesun.load,
     "Galirax": galirax.load,
     "Zevopel": zevopel.load,
+    "Medodra": medodra.load,
 }
 
 
