@@ -250,3 +250,104 @@ def forward(cfg, weights, tokens, state=None, want_layers=False):
     if want_layers:
         return logits, np.stack(streams), state
     return logits, state
+
+
+def logits(cfg, weights, tokens):
+    return forward(cfg, weights, tokens)[0]
+
+
+# ------------------------------------------------------------------------------------------------ small random models for the tests
+def bf16_round(x):
+    u = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32).astype(np.uint64)
+    u = ((u + 0x7FFF + ((u >> 16) & 1)) >> 16) << 16
+    return u.astype(np.uint32).view(np.float32)
+
+
+def moe_cfg(ff=24, experts=6, top=2, shared=16):
+    m = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "top": top}}
+    if shared:
+        m["shared"] = {"ff": shared}
+    return m
+
+
+def delta_layer(heads=4, kv_heads=2, dim=16, vdim=8, conv=4, mlp="moe"):
+    return {"type": "delta", "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "conv": conv}, "mlp": moe_cfg() if mlp == "moe" else mlp}
+
+
+def parallel_layer(heads=4, kv_heads=2, dim=16, vdim=24, conv=3, bias_max=40, coef=0.7, every=16, scale=None, side=48, mlp="moe"):
+    left = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "conv": conv, "bias_max": bias_max, "q_temp": {"coef": coef, "every": every},
+            "scale": scale if scale is not None else 1.0 / math.sqrt(dim)}
+    return {"type": "parallel", "mixer": {"left": left, "right": {"width": side}}, "mlp": moe_cfg() if mlp == "moe" else mlp}
+
+
+def make_config(layers, width=40, vocab=61, eps=1e-5, embed_scale=3.0, residual_mult=0.7, loop=None):
+    cfg = {"architecture": "Medodra", "width": width, "vocab": vocab, "norm": {"eps": eps}, "embedding": {"scale": embed_scale}, "residual_mult": residual_mult, "layers": layers}
+    if loop:
+        cfg["loop"] = {"start": loop[0], "stop": loop[1], "times": loop[2]}
+    return cfg
+
+
+def random_weights(cfg, seed=0, rel_rows=8):
+    """name -> float64 arrays whose values bfloat16 holds exactly, so that the served (bf16) and the exact (f32) modes read the same
+    model."""
+    rng = np.random.default_rng(seed)
+    Wd, Vc = cfg["width"], cfg["vocab"]
+    W = {}
+
+    def mat(name, rows, cols, g=1.0):
+        W[name] = bf16_round(rng.standard_normal((rows, cols)) * g / math.sqrt(cols)).astype(np.float64)
+
+    def vec(name, n, mean=0.0, spread=0.3):
+        W[name] = bf16_round(mean + spread * rng.standard_normal(n)).astype(np.float64)
+
+    W["embed"] = bf16_round(rng.standard_normal((Vc, Wd))).astype(np.float64)
+    mat("head", Vc, Wd, 3.0)
+    vec("final.norm", Wd, 0.0, 0.2)
+    if cfg.get("loop"):
+        mat("loop.in", Wd, 2 * Wd, 1.5)
+    for il, L in enumerate(cfg["layers"]):
+        p, mx = f"l{il}.", L["mixer"]
+        vec(p + "norm1", Wd, 0.0, 0.2)
+        if L["type"] == "delta":
+            H, G, D, V, taps = mx["heads"], mx["kv_heads"], mx["dim"], mx["vdim"], mx["conv"]
+            for leaf, rows in (("q", G * D), ("k", G * D), ("v", H * V)):
+                mat(p + "mix." + leaf, rows, Wd, 1.5)
+                W[p + "mix." + leaf + ".conv"] = bf16_round(rng.standard_normal((rows, taps)) * 0.6).astype(np.float64)
+            mat(p + "mix.b", H, Wd, 2.0); mat(p + "mix.a", H, Wd, 2.0); mat(p + "mix.g", H * V, Wd, 1.5); mat(p + "mix.o", Wd, H * V)
+            vec(p + "mix.A_log", H, -0.5, 0.7); vec(p + "mix.dt_bias", H, 0.0, 1.0); vec(p + "mix.norm", V, 1.0, 0.3)
+        else:
+            a, side = mx["left"], mx["right"]["width"]
+            H, G, D, V, taps = a["heads"], a["kv_heads"], a["dim"], a["vdim"], a["conv"]
+            for leaf, rows in (("q", H * D), ("k", G * D), ("v", G * V)):
+                mat(p + "mix.left." + leaf, rows, Wd, 1.5)
+                vec(p + "mix.left." + leaf + ".b", rows, 0.0, 0.3)
+                W[p + "mix.left." + leaf + ".conv"] = bf16_round(rng.standard_normal((rows, taps)) * 0.6).astype(np.float64)
+            W[p + "mix.left.rel"] = bf16_round(rng.standard_normal((rel_rows, H))).astype(np.float64)
+            vec(p + "mix.left.pb", H, -1.0, 0.7)
+            mat(p + "mix.left.o", Wd, H * V); vec(p + "mix.left.o.b", Wd, 0.0, 0.3)
+            for leaf in ("z", "x", "g"):
+                mat(p + "mix.right." + leaf, side, Wd, 2.0)
+            vec(p + "mix.right.z.b", side, 0.0, 0.5); vec(p + "mix.right.x.b", side, 0.0, 0.5)
+            mat(p + "mix.right.o", Wd, side)
+            vec(p + "mix.left.out", Wd, 1.0, 0.3); vec(p + "mix.right.out", Wd, 1.0, 0.3)
+        mlp = L.get("mlp")
+        if mlp is None:
+            continue
+        vec(p + "norm2", Wd, 0.0, 0.2)
+        F = mlp["expert"]["ff"]
+        for e in range(mlp["router"]["experts"]):
+            mat(p + f"mlp.e{e}.gate", F, Wd, 1.5); mat(p + f"mlp.e{e}.up", F, Wd, 1.5); mat(p + f"mlp.e{e}.down", Wd, F, 1.5)
+        mat(p + "mlp.router", mlp["router"]["experts"], Wd, 3.0)
+        if mlp.get("shared"):
+            FS = mlp["shared"]["ff"]
+            mat(p + "mlp.shared.gate", FS, Wd, 1.5); mat(p + "mlp.shared.up", FS, Wd, 1.5); mat(p + "mlp.shared.down", Wd, FS, 1.5); mat(p + "mlp.shared.sg", 1, Wd, 2.0)
+    return W
+
+
+def as_tensors(W):
+    """name -> (dtype, shape, raw bytes), the form the loader takes: matrices and vectors as bf16 bits."""
+    out = {}
+    for name, a in W.items():
+        bits = (np.ascontiguousarray(a, dtype=np.float32).view(np.uint32) >> 16).astype(np.uint16)
+        out[name] = ("BF16", tuple(a.shape), bits.view(np.uint8).reshape(-1))
+    return out
