@@ -825,6 +825,91 @@ def zevopel_beside_config(size: str) -> dict:
     return {"architecture": "Galirax", "width": W, "vocab": DESIGN_VOCAB, "norm": {"eps": 1e-5}, "logit_softcap": 30.0, "layers": layers}
 
 
+# ------------------------------------------------------------------------------------------------ --design medodra
+# The same measurement for the Medodra design (layers alternating between sigmoid attention beside a minGRU and the gated delta rule,
+# short convolutions on q / k / v, sigmoid-routed experts weighted on their input plus a gated shared expert, one looped stretch with
+# its input projection), beside the closest existing model of the framework: Galirax with alternating attention and lightning (linear
+# attention) layers and routed experts in every layer at equal width, depth, heads and expert size.
+def medodra_config(size: str) -> dict:
+    import math
+    W, (h, g, d, v), (ne, top, ff, _ng, _nk), _window = GALIRAX_SIZES[size]
+    mlp = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": ne, "top": top}, "shared": {"ff": ff}}
+    left = {"heads": h, "kv_heads": g, "dim": d, "vdim": v, "conv": 4, "bias_max": 2048, "q_temp": {"coef": 0.5, "every": 1024}, "scale": 1.0 / math.sqrt(d)}
+    par = {"type": "parallel", "mixer": {"left": left, "right": {"width": W}}, "mlp": mlp}
+    delta = {"type": "delta", "mixer": {"heads": h, "kv_heads": g, "dim": d, "vdim": v, "conv": 4}, "mlp": mlp}
+    return {"architecture": "Medodra", "width": W, "vocab": DESIGN_VOCAB, "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0}, "residual_mult": 0.5,
+            "loop": {"start": 2, "stop": 4, "times": 1}, "layers": [par if il % 2 == 0 else delta for il in range(DESIGN_LAYERS)]}
+
+
+def medodra_random_tensors(cfg: dict):
+    W, V = cfg["width"], cfg["vocab"]
+    t = {"embed": (V, W), "head": (V, W), "final.norm": (W,), "loop.in": (W, 2 * W)}
+    for i, L in enumerate(cfg["layers"]):
+        p, mx = f"l{i}.", L["mixer"]
+        t.update({p + "norm1": (W,), p + "norm2": (W,)})
+        if L["type"] == "delta":
+            H, G, D, Vd, taps = mx["heads"], mx["kv_heads"], mx["dim"], mx["vdim"], mx["conv"]
+            t.update({p + "mix.q": (G * D, W), p + "mix.k": (G * D, W), p + "mix.v": (H * Vd, W), p + "mix.q.conv": (G * D, taps), p + "mix.k.conv": (G * D, taps),
+                      p + "mix.v.conv": (H * Vd, taps), p + "mix.b": (H, W), p + "mix.a": (H, W), p + "mix.g": (H * Vd, W), p + "mix.o": (W, H * Vd), p + "mix.A_log": (H,),
+                      p + "mix.dt_bias": (H,), p + "mix.norm": (Vd,)})
+        else:
+            a, side = mx["left"], mx["right"]["width"]
+            H, G, D, Vd, taps = a["heads"], a["kv_heads"], a["dim"], a["vdim"], a["conv"]
+            for leaf, rows in (("q", H * D), ("k", G * D), ("v", G * Vd)):
+                t.update({p + "mix.left." + leaf: (rows, W), p + "mix.left." + leaf + ".b": (rows,), p + "mix.left." + leaf + ".conv": (rows, taps)})
+            t.update({p + "mix.left.rel": (32, H), p + "mix.left.pb": (H,), p + "mix.left.o": (W, H * Vd), p + "mix.left.o.b": (W,), p + "mix.right.z": (side, W),
+                      p + "mix.right.z.b": (side,), p + "mix.right.x": (side, W), p + "mix.right.x.b": (side,), p + "mix.right.g": (side, W), p + "mix.right.o": (W, side),
+                      p + "mix.left.out": (W,), p + "mix.right.out": (W,)})
+        E, F, FS = L["mlp"]["router"]["experts"], L["mlp"]["expert"]["ff"], L["mlp"]["shared"]["ff"]
+        t.update({p + "mlp.router": (E, W), p + "mlp.shared.gate": (FS, W), p + "mlp.shared.up": (FS, W), p + "mlp.shared.down": (W, FS), p + "mlp.shared.sg": (1, W)})
+        for e in range(E):
+            t.update({f"{p}mlp.e{e}.gate": (F, W), f"{p}mlp.e{e}.up": (F, W), f"{p}mlp.e{e}.down": (W, F)})
+    out = random_tensors(t)
+    for name, (dt, shape, raw) in list(out.items()):
+        leaf = name.split(".")[-1]
+        if leaf in ("norm1", "norm2") or name == "final.norm":  # stored as the distance from one
+            out[name] = (dt, shape, np.zeros(int(np.prod(shape)), np.float32).view(np.uint8))
+        elif leaf == "out":
+            out[name] = (dt, shape, np.full(int(np.prod(shape)), 1.0, np.float32).view(np.uint8))
+    return out
+
+
+def medodra_step_cost(cfg: dict, n_tokens: int, n_seq: int, ctx: int) -> dict:
+    """Algorithmic bytes (bf16 weights once -- of the experts those a batch of this size can reach --, the f32 cache rows and recurrent
+    states of the batch) and FLOPs of one step."""
+    W, V = cfg["width"], cfg["vocab"]
+    wparams = active = W * V + 2 * W * W  # head, loop.in (the stretch runs once)
+    cache = state = attn_flop = 0
+    for L in cfg["layers"]:
+        mx = L["mixer"]
+        if L["type"] == "delta":
+            H, G, D, Vd = mx["heads"], mx["kv_heads"], mx["dim"], mx["vdim"]
+            p = W * (2 * G * D + 2 * H * Vd + 2 * H) + W * H * Vd
+            state += n_seq * H * D * Vd * 4 * 2
+            attn_flop += 6 * n_tokens * H * D * Vd
+        else:
+            a, side = mx["left"], mx["right"]["width"]
+            H, G, D, Vd = a["heads"], a["kv_heads"], a["dim"], a["vdim"]
+            p = W * (H * D + G * D + G * Vd + 3 * side) + W * H * Vd + W * side
+            cache += n_seq * ctx * G * (D + Vd) * 4
+            attn_flop += 2 * n_tokens * H * (ctx if n_tokens == n_seq else ctx // 2) * (D + Vd)
+        r, F, FS = L["mlp"]["router"], L["mlp"]["expert"]["ff"], L["mlp"]["shared"]["ff"]
+        wparams += p + W * r["experts"] + 3 * W * F * min(r["experts"], n_tokens * r["top"]) + 3 * W * FS + W
+        active += p + W * r["experts"] + 3 * W * F * r["top"] + 3 * W * FS + W
+    return {"weight_bytes": 2 * wparams, "cache_bytes": cache, "state_bytes": state, "flop": 2 * active * n_tokens + attn_flop}
+
+
+def medodra_beside_config(size: str) -> dict:
+    """Galirax at equal width, depth, heads and expert size: attention (sink, no window) and lightning layers in turn, routed experts in every layer."""
+    import math
+    W, (h, g, d, v), (ne, top, ff, ng, nk), _window = GALIRAX_SIZES[size]
+    mlp = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": ne, "top": top, "groups": {"count": ng, "keep": nk}, "scale": 2.0}}
+    rot = {"base": 500000.0, "dims": d // 2}
+    att = {"type": "attention", "mixer": {"heads": h, "kv_heads": g, "dim": d, "vdim": v, "rot": rot, "scale": 1.0 / math.sqrt(d)}, "mlp": mlp}
+    lin = {"type": "lightning", "mixer": {"heads": h, "dim": d, "vdim": v, "decay": [1.0 - 2.0 ** (-5 - 3 * i / h) for i in range(h)]}, "mlp": mlp}
+    return {"architecture": "Galirax", "width": W, "vocab": DESIGN_VOCAB, "norm": {"eps": 1e-5}, "logit_softcap": 30.0, "layers": [att if il % 2 == 0 else lin for il in range(DESIGN_LAYERS)]}
+
+
 def galirax_llama_shape(size: str):
     import koboldcpp_b200.llama as LL
     W, (h, g, d, v), (ne, top, ff, ng, nk), window = GALIRAX_SIZES[size]
@@ -862,8 +947,12 @@ def random_tensors(shapes: dict, seed: int = 1):
 
 
 def design_table():
-    from koboldcpp_b200 import galirax, genesun, zevopel
+    from koboldcpp_b200 import galirax, genesun, medodra, zevopel
     return {
+        "medodra": {"sizes": GALIRAX_SIZES, "config": medodra_config, "tensors": medodra_random_tensors, "cost": medodra_step_cost, "build": medodra.build,
+                    "beside_design": {"name": "galirax", "config": medodra_beside_config, "tensors": lambda cfg: random_tensors(galirax_tensor_shapes(cfg)),
+                                      "cost": galirax_step_cost, "build": galirax.build},
+                    "beside": "Galirax (attention with sinks and lightning layers in turn, routed experts in every layer), equal width / depth / heads / expert size, bf16"},
         "zevopel": {"sizes": GALIRAX_SIZES, "config": zevopel_config, "tensors": zevopel_random_tensors, "cost": zevopel_step_cost, "build": zevopel.build,
                     "beside_design": {"name": "galirax", "config": zevopel_beside_config, "tensors": lambda cfg: random_tensors(galirax_tensor_shapes(cfg)),
                                       "cost": galirax_step_cost, "build": galirax.build},
@@ -995,7 +1084,7 @@ def main() -> int:
     ap.add_argument("--cpu-budget", type=float, default=18.0)
     ap.add_argument("--no-tp70", action="store_true", default=bool(os.environ.get("B200_BENCH_NO_TP70")),
                     help="skip the auxiliary 70B tensor-parallel leg (BASELINE.json configs[4])")
-    ap.add_argument("--design", default="", choices=["", "genesun", "galirax", "zevopel"],
+    ap.add_argument("--design", default="", choices=["", "genesun", "galirax", "zevopel", "medodra"],
                     help="instead of the default workload: prefill / decode of this design at real layer shapes beside the closest existing model at equal size")
     ap.add_argument("--design-sizes", default="", help="comma-separated subset of the sizes of the design (genesun: " + ",".join(DESIGN_SIZES) + "; the others: " + ",".join(GALIRAX_SIZES) + ")")
     args = ap.parse_args()

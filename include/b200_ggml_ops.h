@@ -126,7 +126,7 @@ enum b200_ext_op {
                                   by its root mean square, [10] q temperature coefficient, [11] its period in positions; freqs may be NULL without rotation */
     B200_EXT_SINK_ATTN = 10,   /* src: q, k cache, v cache, sink, tok_seq, tok_pos, cell_seq, cell_pos, [head gate [heads, T]]; op_params: [2] dim, [3] scale,
                                   [4] window, [5] keep_first, [6] bf16 products, [7] vdim, [8] chunk, [9] enum b200_attn_weights; src[9]: score bias by distance
-                                  [heads, n_dist] (optional) */
+                                  [n_dist, heads] (optional) */
     B200_EXT_LINEAR_ATTN_SCAN = 11, /* src: q, k, v, decay, seq_info, state; op_params: [2] heads, [3] dim, [4] vdim, [5] silu on q / k / v */
     B200_EXT_MOE_ROUTE = 12,   /* src: logits, correction; dst [2 n_used, T]: per token n_used weights (f32), then n_used expert ids (i32);
                                   op_params: [2] n_group, [3] n_group_used, [4] scale, [5] n_used, [6] enum b200_router_score, [7] weights are the
@@ -282,7 +282,7 @@ typedef struct {
     int32_t chunk;
     const float *gate; int64_t gate_stride;
     int32_t weights;                       /* enum b200_attn_weights */
-    const float *dist_bias; int32_t n_dist; /* [n_dist][n_head] added to the scaled score of a key min(tok_pos - cell_pos, n_dist - 1) positions back (NULL: none) */
+    const float *dist_bias; int32_t n_dist; /* [n_head][n_dist] added to the scaled score of a key min(tok_pos - cell_pos, n_dist - 1) positions back (NULL: none) */
 } b200_sink_attn_args;
 B200_API int b200_op_sink_attn(const b200_sink_attn_args *a, b200_stream_t stream);
 /* The same with a workspace of b200_sink_attn_workspace_bytes(a) bytes (16-byte aligned; 0: none needed): with few tokens and
@@ -345,7 +345,7 @@ B200_API int b200_op_add_sinusoid(const b200_tensor *x, const int32_t *pos, cons
 /* Short causal convolution over time, every channel by itself: y[t] = act(sum_j w[c][j] * u[t - taps + 1 + j]), u = x + bias, zeros before
  * the start of a sequence.  The last taps - 1 values of u of a sequence wait in its slot of `tail` ([taps - 1][channels] per slot) for
  * its next tokens.  seq_info as for b200_op_mlstm_scan.  x, dst [n_tokens][channels] (not the same memory), strides in floats; w
- * [channels][taps]; taps <= 33. */
+ * [channels][taps]; taps <= 17. */
 typedef struct {
     const float *x; int64_t x_stride;
     const float *bias;                     /* [channels] or NULL */

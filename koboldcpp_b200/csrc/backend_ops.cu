@@ -77,7 +77,7 @@ static bool ext_op_supported(const ggml_tensor *op) {
             return f32_rows(s[0]) && f32_rows(s[1]) && f32_rows(s[2]) && (!s[3] || f32_vec(s[3])) && i32_vec(s[4]) && i32_vec(s[5]) && i32_vec(s[6]) && i32_vec(s[7]) &&
                    f32_rows(op) && op->op_params[2] > 0 && op->op_params[2] <= 256 && op->op_params[7] > 0 && op->op_params[7] <= 256 && s[0]->ne[0] % op->op_params[2] == 0 &&
                    (!s[8] || (f32_rows(s[8]) && s[8]->ne[0] == s[0]->ne[0] / op->op_params[2] && s[8]->ne[1] == s[0]->ne[1])) &&
-                   (!s[9] || (f32_vec(s[9]) && s[9]->ne[0] == s[0]->ne[0] / op->op_params[2] && s[9]->ne[1] > 0));
+                   (!s[9] || (f32_vec(s[9]) && s[9]->ne[1] == s[0]->ne[0] / op->op_params[2] && s[9]->ne[0] > 0));
         case B200_EXT_LINEAR_ATTN_SCAN:
             return f32_rows(s[0]) && f32_rows(s[1]) && f32_rows(s[2]) && f32_vec(s[3]) && i32_vec(s[4]) && f32_rows(s[5]) && f32_rows(op) && op->op_params[3] <= 256;
         case B200_EXT_MOE_ROUTE:
@@ -100,7 +100,7 @@ static bool ext_op_supported(const ggml_tensor *op) {
             return f32_rows(s[0]) && f32_rows(op) && same_shape(s[0], op) && op->ne[2] == 1 && op->ne[3] == 1 && i32_vec(s[1]) && s[1]->ne[0] >= op->ne[1] && f32_vec(s[2]) &&
                    s[2]->ne[0] >= (op->ne[0] + 1) / 2;
         case B200_EXT_SHORT_CONV:
-            return f32_rows(s[0]) && f32_rows(op) && same_shape(s[0], op) && f32_vec(s[1]) && s[1]->ne[1] == op->ne[0] && s[1]->ne[0] >= 1 && s[1]->ne[0] <= 33 &&
+            return f32_rows(s[0]) && f32_rows(op) && same_shape(s[0], op) && f32_vec(s[1]) && s[1]->ne[1] == op->ne[0] && s[1]->ne[0] >= 1 && s[1]->ne[0] <= 17 &&
                    (!s[2] || (f32_vec(s[2]) && s[2]->ne[0] == op->ne[0])) && i32_vec(s[3]) && f32_rows(s[4]) && s[4]->ne[0] >= (s[1]->ne[0] - 1) * op->ne[0];
         case B200_EXT_DELTA_RULE_SCAN:
             for (int i = 0; i < 5; i++) if (!f32_rows(s[i])) return false;
@@ -128,7 +128,7 @@ static void fill_sink_attn_args(const ggml_tensor *n, b200_sink_attn_args &a) {
     a.chunk = n->op_params[8];
     if (s[8]) { a.gate = (const float *)s[8]->data; a.gate_stride = (int64_t)(s[8]->nb[1] / 4); }
     a.weights = n->op_params[9];
-    if (s[9]) { a.dist_bias = (const float *)s[9]->data; a.n_dist = (int32_t)s[9]->ne[1]; }
+    if (s[9]) { a.dist_bias = (const float *)s[9]->data; a.n_dist = (int32_t)s[9]->ne[0]; }
 }
 
 // the batched tensor-core form of an expert product over bf16 weights (the grouped GEMM of the quantised types)

@@ -102,9 +102,11 @@ __device__ __forceinline__ bool sa_visible(int cell_seq, int cell_pos, int seq, 
 __device__ __forceinline__ int sa_chunk_start(int pos, int chunk) { return chunk > 0 ? pos - pos % chunk : 0; }
 // the bias of a key `dist` positions behind the query (0 without a table)
 __device__ __forceinline__ float sa_dist_bias(const b200_sink_attn_args &a, int dist, int h) {
-    return a.dist_bias ? a.dist_bias[(int64_t)min(dist, a.n_dist - 1) * a.n_head + h] : 0.f;
+    return a.dist_bias ? a.dist_bias[(int64_t)h * a.n_dist + min(dist, a.n_dist - 1)] : 0.f;  // a head's row is contiguous: neighbouring keys share cache lines
 }
 __device__ __forceinline__ float sa_sigmoid(float x) { return 1.0f / (1.0f + expf(-x)); }
+// for weights that are rounded to bf16 right away (8 bits of mantissa): the fast exponential and division are exact enough
+__device__ __forceinline__ float sa_sigmoid_fast(float x) { return __fdividef(1.0f, 1.0f + __expf(-x)); }
 __device__ __forceinline__ float sa_head_gate(const b200_sink_attn_args &a, int64_t t, int h) {
     return a.gate ? 1.0f / (1.0f + expf(-a.gate[t * a.gate_stride + h])) : 1.0f;
 }
@@ -426,8 +428,8 @@ __global__ void __launch_bounds__(GM_WARPS * 32) sink_attn_mma_kernel(const b200
             unsigned pa[GM_CELLS / 16][4];
 #pragma unroll
             for (int j = 0; j < GM_CELLS / 8; j++) {
-                pa[j >> 1][(j & 1) * 2] = gm_pack_bf2(sa_sigmoid(s[j][0]), sa_sigmoid(s[j][1]));
-                pa[j >> 1][(j & 1) * 2 + 1] = gm_pack_bf2(sa_sigmoid(s[j][2]), sa_sigmoid(s[j][3]));
+                pa[j >> 1][(j & 1) * 2] = gm_pack_bf2(sa_sigmoid_fast(s[j][0]), sa_sigmoid_fast(s[j][1]));
+                pa[j >> 1][(j & 1) * 2 + 1] = gm_pack_bf2(sa_sigmoid_fast(s[j][2]), sa_sigmoid_fast(s[j][3]));
             }
 #pragma unroll
             for (int kk = 0; kk < GM_CELLS / 16; kk++) {

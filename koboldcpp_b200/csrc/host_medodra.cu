@@ -29,7 +29,7 @@ namespace {
 constexpr float kUnitEps = 1e-6f;  // q and k of the delta rule: x / sqrt(sum(x^2) + 1e-6)
 
 struct MdLayer {
-    ggml_tensor *pre1 = nullptr, *pre2 = nullptr;      // 1 + norm1, 1 + norm2
+    ggml_tensor *pre1 = nullptr, *pre12 = nullptr;     // 1 + norm1 alone (no feed-forward), or 1 + norm1 over 1 + norm2 as one [2][width] tensor
     ggml_tensor *proj1 = nullptr, *convw = nullptr, *convb = nullptr, *wo = nullptr;
     int64_t proj1_rows = 0, conv_channels = 0;
     // delta
@@ -59,7 +59,6 @@ MdData *md(b200_llama *m) {
 
 int64_t pad8(int64_t v) { return (v + 7) / 8 * 8; }
 bool is_delta(const b200_layer_params &lp) { return lp.mixer == B200_MIXER_DELTA; }
-const char *mix_prefix(const b200_layer_params &lp) { return is_delta(lp) ? "mix." : "mix.left."; }
 // everything the mixer projects from its input, in the order of the rows of the fused matrix; q, k, v come first
 int parts_proj1(const b200_layer_params &lp, Part out[8]) {
     int n = 0;
@@ -238,9 +237,19 @@ int md_finalize(b200_llama *m) {
         const int64_t H = lp.heads, G = lp.kv_heads, D = lp.dim, V = lp.vdim;
         LL_REQUIRE(H > 0 && G > 0 && H % G == 0 && D > 0 && D <= 256 && V > 0 && V <= 256, B200_ERR_INVALID, "b200_llama_finalize: layer %d: heads %d over %d kv heads, dim %d and vdim %d (<= 256)", il,
                    lp.heads, lp.kv_heads, lp.dim, lp.vdim);
-        LL_REQUIRE(lp.conv_taps >= 1 && lp.conv_taps <= 33, B200_ERR_UNSUPPORTED, "b200_llama_finalize: layer %d: a convolution of 1 to 33 taps", il);
+        LL_REQUIRE(lp.conv_taps >= 1 && lp.conv_taps <= 17, B200_ERR_UNSUPPORTED, "b200_llama_finalize: layer %d: a convolution of 1 to 17 taps", il);
         any_loop |= lp.loop_input != 0;
-        rc = fold(pre + "pre1", pre + "norm1", 1.0f, 1.0f, W, &L.pre1);
+        if (lp.mlp == B200_MLP_NONE) {
+            rc = fold(pre + "pre1", pre + "norm1", 1.0f, 1.0f, W, &L.pre1);
+        } else {  // both norms read the same row: one launch over [width, 2, tokens] with the weight chosen by the middle index
+            auto n1 = g->host_vecs.find(pre + "norm1"), n2 = g->host_vecs.find(pre + "norm2");
+            LL_REQUIRE(n1 != g->host_vecs.end() && n2 != g->host_vecs.end() && (int64_t)n1->second.size() == W && (int64_t)n2->second.size() == W, B200_ERR_INVALID,
+                       "b200_llama_finalize: %snorm1 / norm2 missing or not %lld values", pre.c_str(), (long long)W);
+            std::vector<float> v((size_t)(2 * W));
+            for (int64_t i = 0; i < W; i++) { v[(size_t)i] = 1.0f + n1->second[(size_t)i]; v[(size_t)(W + i)] = 1.0f + n2->second[(size_t)i]; }
+            rc = upload_tensor(m, (pre + "pre12").c_str(), GGML_TYPE_F32, W, 2, 1, v.data());
+            L.pre12 = find_w(m, pre + "pre12");
+        }
         if (rc != B200_OK) return rc;
         Part parts[8];
         int np = parts_proj1(lp, parts);
@@ -275,7 +284,7 @@ int md_finalize(b200_llama *m) {
             if (rc != B200_OK) return rc;
             rc = fold(pre + "mix.out_r", pre + "mix.right.out", 0.0f, 0.5f, W, &L.out_r);
             if (rc != B200_OK) return rc;
-            // rel[bucket(n)][h] + pb[h] for n = 0 .. bias_max; the last row serves every greater distance
+            // per head rel[bucket(n)][h] + pb[h] for n = 0 .. bias_max; the last entry serves every greater distance
             auto rel = g->host_vecs.find(pre + "mix.left.rel"), pb = g->host_vecs.find(pre + "mix.left.pb");
             LL_REQUIRE(rel != g->host_vecs.end() && pb != g->host_vecs.end() && (int64_t)pb->second.size() == H, B200_ERR_INVALID, "b200_llama_finalize: %smix.left.rel / pb missing", pre.c_str());
             const int64_t rows = g->host_rows[pre + "mix.left.rel"], far = lp.dist_bias_max;
@@ -283,16 +292,14 @@ int md_finalize(b200_llama *m) {
                        "b200_llama_finalize: layer %d: a distance table of [rows >= 2, %lld] with the farthest distance beyond rows / 2", il, (long long)H);
             std::vector<float> tab((size_t)((far + 1) * H));
             for (int64_t n = 0; n <= far; n++)
-                for (int64_t h = 0; h < H; h++) tab[(size_t)(n * H + h)] = rel->second[(size_t)(distance_bucket(n, rows, far) * H + h)] + pb->second[(size_t)h];
-            rc = upload_tensor(m, (pre + "mix.dist").c_str(), GGML_TYPE_F32, H, far + 1, 1, tab.data());
+                for (int64_t h = 0; h < H; h++) tab[(size_t)(h * (far + 1) + n)] = rel->second[(size_t)(distance_bucket(n, rows, far) * H + h)] + pb->second[(size_t)h];
+            rc = upload_tensor(m, (pre + "mix.dist").c_str(), GGML_TYPE_F32, far + 1, H, 1, tab.data());
             if (rc != B200_OK) return rc;
             L.dist = find_w(m, pre + "mix.dist");
         }
         if (lp.mlp == B200_MLP_NONE) continue;
         LL_REQUIRE(lp.mlp == B200_MLP_MOE_GATED && lp.ff > 0 && lp.n_expert > 0 && lp.n_expert <= 256 && lp.n_expert_used > 0 && lp.n_expert_used <= 32 && lp.n_expert_used <= lp.n_expert,
                    B200_ERR_UNSUPPORTED, "b200_llama_finalize: layer %d: feed-forward kind / expert counts (at most 256 experts, 32 per token)", il);
-        rc = fold(pre + "pre2", pre + "norm2", 1.0f, 1.0f, W, &L.pre2);
-        if (rc != B200_OK) return rc;
         for (int e = 0; e < lp.n_expert; e++)
             for (const char *w : {"gate", "up", "down"}) {
                 const std::string nm = pre + "mlp.e" + std::to_string(e) + "." + w;
@@ -400,7 +407,17 @@ int md_build(b200_llama *m, const BatchShape &bs) {
             both->data = cat->data; both->view_src = cat; both->view_offs = 0;
             x = b.mul_mat(g->loop_in, both);
         }
-        ggml_tensor *h1 = norm(x, L.pre1);
+        ggml_tensor *h1, *h2 = nullptr, *h2_3d = nullptr;
+        if (L.pre12) {
+            ggml_tensor *hh = b.alloc_result(GGML_TYPE_F32, W, 2, T);
+            b.ext(hh, B200_EXT_NORM, {b.view_3d(x, W, 2, T, 0, x->nb[1], 0), L.pre12, nullptr, nullptr, nullptr, nullptr});
+            hh->op_params[2] = B200_NORM_RMS; Builder::set_f(hh, 3, eps); hh->op_params[4] = 2; hh->op_params[5] = 0;
+            h1 = b.view_2d(hh, W, T, hh->nb[2], 0);
+            h2 = b.view_2d(hh, W, T, hh->nb[2], (size_t)W * 4);
+            h2_3d = b.view_3d(hh, W, 1, T, hh->nb[2], hh->nb[2], (size_t)W * 4);
+        } else {
+            h1 = norm(x, L.pre1);
+        }
         ggml_tensor *P = b.mul_mat(L.proj1, h1);
         Part parts[8];
         const int np = parts_proj1(lp, parts);
@@ -452,7 +469,6 @@ int md_build(b200_llama *m, const BatchShape &bs) {
         ggml_tensor *nx = next_starts ? rows_of(cat, 0, W) : b.alloc_result(GGML_TYPE_F32, W, T);
         if (lp.mlp == B200_MLP_MOE_GATED) {
             const int64_t F = lp.ff, NU = lp.n_expert_used;
-            ggml_tensor *h2 = norm(x, L.pre2);
             // the router's result: per token NU weights, then NU expert ids (as i32) in the same row
             ggml_tensor *rt = b.alloc_result(GGML_TYPE_F32, 2 * NU, T);
             b.ext(rt, B200_EXT_MOE_ROUTE, {b.mul_mat(L.router, h2), nullptr});
@@ -460,7 +476,7 @@ int md_build(b200_llama *m, const BatchShape &bs) {
             rt->op_params[6] = lp.router_score; rt->op_params[7] = lp.router_keep_scores ? 1 : 0;
             ggml_tensor *wts = b.view_2d(rt, NU, T, rt->nb[1], 0), *ids = b.view_2d(rt, NU, T, rt->nb[1], (size_t)NU * 4);
             ids->type = GGML_TYPE_I32;
-            ggml_tensor *gu = b.ext(b.alloc_result(GGML_TYPE_F32, 2 * F, NU, T), B200_EXT_MUL_MAT_ID, {L.gate_up, b.reshape(h2, W, 1, T), ids});
+            ggml_tensor *gu = b.ext(b.alloc_result(GGML_TYPE_F32, 2 * F, NU, T), B200_EXT_MUL_MAT_ID, {L.gate_up, h2_3d, ids});
             // an expert's weight scales its input: the same factor on both of its linear products, applied where they are read
             ggml_tensor *act = b.ext(b.alloc_result(GGML_TYPE_F32, F, NU, T), B200_EXT_SILU_MUL,
                                      {b.view_3d(gu, F, NU, T, gu->nb[1], gu->nb[2], 0), b.view_3d(gu, F, NU, T, gu->nb[1], gu->nb[2], (size_t)F * 4), lp.router_scale_input ? wts : nullptr});

@@ -215,21 +215,52 @@ __global__ void moe_combine_kernel(const float *__restrict__ y, int64_t y_s_slot
 }
 
 // The chosen experts' results (weights optional), a shared expert's result times the sigmoid of its per-token gate logit, the other
-// sublayer's result; their sum times the residual multiplier joins the stream.
+// sublayer's result; their sum times the residual multiplier joins the stream.  VEC values per thread (4: 16-byte loads and stores).
+template <int VEC>
 __global__ void moe_combine_shared_kernel(const float *__restrict__ y, int64_t y_s_slot, int64_t y_s_tok, const float *__restrict__ w, int64_t w_s_tok,
                                           const float *__restrict__ add0, int64_t add0_stride, const float *__restrict__ add1, int64_t add1_stride,
                                           const float *__restrict__ shared, int64_t shared_stride, const float *__restrict__ gate, int64_t gate_stride, float mult,
                                           float *__restrict__ dst, int64_t dst_stride, int64_t n, int n_used, int64_t total) {
-    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int64_t idx = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * VEC;
     if (idx >= total) return;
     const int64_t t = idx / n, i = idx - t * n;
-    float s = 0.f;
-    for (int k = 0; k < n_used; k++) s += (w ? w[t * w_s_tok + k] : 1.0f) * y[t * y_s_tok + k * y_s_slot + i];
-    if (shared) s += shared[t * shared_stride + i] * (gate ? sigmoidf_(gate[t * gate_stride]) : 1.0f);
-    if (add1) s += add1[t * add1_stride + i];
-    s *= mult;
-    if (add0) s += add0[t * add0_stride + i];
-    dst[t * dst_stride + i] = s;
+    float s[VEC];
+    auto load = [&](const float *p, float (&v)[VEC]) {
+        if (VEC == 4) { const float4 q = *reinterpret_cast<const float4 *>(p); v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w; }
+        else v[0] = *p;
+    };
+#pragma unroll
+    for (int e = 0; e < VEC; e++) s[e] = 0.f;
+    for (int k = 0; k < n_used; k++) {
+        float v[VEC];
+        load(y + t * y_s_tok + k * y_s_slot + i, v);
+        const float wk = w ? w[t * w_s_tok + k] : 1.0f;
+#pragma unroll
+        for (int e = 0; e < VEC; e++) s[e] += wk * v[e];
+    }
+    if (shared) {
+        float v[VEC];
+        load(shared + t * shared_stride + i, v);
+        const float gs = gate ? sigmoidf_(gate[t * gate_stride]) : 1.0f;
+#pragma unroll
+        for (int e = 0; e < VEC; e++) s[e] += gs * v[e];
+    }
+    if (add1) {
+        float v[VEC];
+        load(add1 + t * add1_stride + i, v);
+#pragma unroll
+        for (int e = 0; e < VEC; e++) s[e] += v[e];
+    }
+#pragma unroll
+    for (int e = 0; e < VEC; e++) s[e] *= mult;
+    if (add0) {
+        float v[VEC];
+        load(add0 + t * add0_stride + i, v);
+#pragma unroll
+        for (int e = 0; e < VEC; e++) s[e] += v[e];
+    }
+    if (VEC == 4) *reinterpret_cast<float4 *>(dst + t * dst_stride + i) = make_float4(s[0], s[1], s[2], s[3]);
+    else dst[t * dst_stride + i] = s[0];
 }
 
 // The weighted sum of a token's expert results, an RMS norm over it with a weight, and the residual stream, one CTA per token.
@@ -384,8 +415,15 @@ extern "C" int b200_op_moe_combine_shared(const float *y, int64_t y_s_slot, int6
     OPX_REQUIRE(dst && n >= 0 && n_used >= 0 && n_tok >= 0 && (y || n_used == 0), B200_ERR_INVALID, "b200_op_moe_combine_shared: bad argument");
     const int64_t total = n * n_tok;
     if (total == 0) return B200_OK;
-    moe_combine_shared_kernel<<<grid1d(total, 256), 256, 0, (cudaStream_t)stream>>>(y, y_s_slot, y_s_tok, w, w_s_tok, add0, add0_stride, add1, add1_stride, shared, shared_stride,
-                                                                                   gate, gate_stride, mult, dst, dst_stride, n, n_used, total);
+    // 16-byte accesses when every row of every operand starts on a 16-byte boundary
+    auto al = [](const float *p, int64_t stride) { return !p || ((((uintptr_t)p) & 15) == 0 && stride % 4 == 0); };
+    const bool vec = n % 4 == 0 && al(y, y_s_slot) && y_s_tok % 4 == 0 && al(add0, add0_stride) && al(add1, add1_stride) && al(shared, shared_stride) && al(dst, dst_stride);
+    if (vec)
+        moe_combine_shared_kernel<4><<<grid1d(total / 4, 256), 256, 0, (cudaStream_t)stream>>>(y, y_s_slot, y_s_tok, w, w_s_tok, add0, add0_stride, add1, add1_stride, shared,
+                                                                                          shared_stride, gate, gate_stride, mult, dst, dst_stride, n, n_used, total);
+    else
+        moe_combine_shared_kernel<1><<<grid1d(total, 256), 256, 0, (cudaStream_t)stream>>>(y, y_s_slot, y_s_tok, w, w_s_tok, add0, add0_stride, add1, add1_stride, shared,
+                                                                                      shared_stride, gate, gate_stride, mult, dst, dst_stride, n, n_used, total);
     B200_CUDA_TRY(cudaGetLastError());
     return B200_OK;
 }

@@ -15,7 +15,11 @@ __device__ __forceinline__ float softplus_f(float x) { return fmaxf(x, 0.f) + lo
 // (+ bias) for i >= 0 and the tail's entry taps - 1 + i before that; only the CTA of the portion's first tokens reads the tail, and
 // it alone rewrites it afterwards (thread = channel, so nobody else touches the same values): the new tail is the last taps - 1
 // inputs, which are old tail entries shifted down where the portion is shorter than the tail.
-constexpr int SC_TOK = 32, SC_MAX_TAPS = SC_TOK + 1;
+// KMAX >= taps is the compile-time window: the weights are padded with zeros in front, the SC_TOK + KMAX - 1 inputs of the CTA's
+// tokens travel to registers with all loads in flight at once, and every output is KMAX multiply-adds on registers.  KMAX == 0 is
+// the general form for longer filters (every input read where it is used).
+constexpr int SC_TOK = 16, SC_MAX_TAPS = SC_TOK + 1;
+template <int KMAX>
 __global__ void __launch_bounds__(128) short_conv_kernel(const b200_short_conv_args a) {
     const int c = blockIdx.x * 128 + threadIdx.x, s = blockIdx.z;
     const int first = a.seq_info[s], count = a.seq_info[a.n_seq + s], slot = a.seq_info[2 * a.n_seq + s], fresh = a.seq_info[3 * a.n_seq + s];
@@ -27,12 +31,27 @@ __global__ void __launch_bounds__(128) short_conv_kernel(const b200_short_conv_a
     const float *w = a.w + (int64_t)c * taps;
     auto input = [&](int i) -> float {
         if (i >= 0) return a.x[(int64_t)(first + i) * a.x_stride + c] + bias;
-        return fresh ? 0.f : tail[(int64_t)(taps - 1 + i) * a.channels];
+        return (fresh || i < -(taps - 1)) ? 0.f : tail[(int64_t)(taps - 1 + i) * a.channels];
     };
-    for (int t = t0; t < t0 + nt; t++) {
-        float y = 0.f;
-        for (int j = 0; j < taps; j++) y += w[j] * input(t - taps + 1 + j);
-        a.dst[(int64_t)(first + t) * a.dst_stride + c] = a.act ? silu_f(y) : y;
+    if (KMAX > 0) {
+        float wp[KMAX > 0 ? KMAX : 1], win[SC_TOK + (KMAX > 0 ? KMAX : 1) - 1];
+#pragma unroll
+        for (int j = 0; j < KMAX; j++) wp[j] = j >= KMAX - taps ? w[j - (KMAX - taps)] : 0.f;
+#pragma unroll
+        for (int i = 0; i < SC_TOK + KMAX - 1; i++) win[i] = i - (KMAX - 1) < nt ? input(t0 + i - (KMAX - 1)) : 0.f;  // win[i] = input t0 + i - (KMAX - 1)
+#pragma unroll
+        for (int t = 0; t < SC_TOK; t++) {
+            float y = 0.f;
+#pragma unroll
+            for (int j = 0; j < KMAX; j++) y += wp[j] * win[t + j];
+            if (t < nt) a.dst[(int64_t)(first + t0 + t) * a.dst_stride + c] = a.act ? silu_f(y) : y;
+        }
+    } else {
+        for (int t = t0; t < t0 + nt; t++) {
+            float y = 0.f;
+            for (int j = 0; j < taps; j++) y += w[j] * input(t - taps + 1 + j);
+            a.dst[(int64_t)(first + t) * a.dst_stride + c] = a.act ? silu_f(y) : y;
+        }
     }
     if (t0 == 0) {
         // entry j of the new tail is input count - (taps - 1) + j: an old entry of higher index, or a value of x; ascending j never
@@ -165,49 +184,53 @@ static int launch_delta_rule(const b200_delta_rule_args *a, cudaStream_t st) {
 
 // ------------------------------------------------------------------------------------------------ minGRU
 // S_t = (1 - z_t) S_(t-1) + z_t c_t is linear in S, so a stretch of tokens acts on the state as S -> A S + B.  A CTA takes 32
-// channels of one sequence; its MG_SEG warp-rows cut the sequence's tokens into MG_SEG stretches: every stretch first finds its
-// (A, B), the stretches' starting states follow one after the other through shared memory, and the stretch is run again from its
-// true starting state to write the outputs.  With few tokens (decoding) there is one stretch and a single pass.
-constexpr int MG_SEG = 8;
-__device__ __forceinline__ void mingru_gates(const b200_mingru_args &a, int64_t tok, int c, float zb, float xb, float &z, float &cand) {
-    z = sigmoidf_(a.z[tok * a.z_stride + c] + zb);
-    const float u = a.x[tok * a.x_stride + c] + xb;
-    cand = u >= 0.f ? u + 0.5f : sigmoidf_(u);
-}
-__global__ void __launch_bounds__(32 * MG_SEG) mingru_scan_kernel(const b200_mingru_args a) {
-    __shared__ float sA[MG_SEG][32], sB[MG_SEG][32];
-    const int c = blockIdx.x * 32 + (threadIdx.x & 31), seg = threadIdx.x >> 5, s = blockIdx.y;
+// channels of one sequence (a warp row reads 128 contiguous bytes of a token) and blockDim.y stretches of MG_TPT tokens at a time:
+// every thread loads its stretch with all loads in flight, turns the pre-activations into gates once, finds its (A, B), reads the
+// state in front of its stretch off the earlier stretches' (A, B) in shared memory, and runs its tokens again from registers to
+// write the outputs.  With few tokens (decoding) the launch has one stretch per CTA and the middle step is empty.
+constexpr int MG_TPT = 8, MG_SEG_MAX = 32;
+__global__ void __launch_bounds__(32 * MG_SEG_MAX) mingru_scan_kernel(const b200_mingru_args a) {
+    __shared__ float sA[MG_SEG_MAX][32], sB[MG_SEG_MAX][32], sS[32];
+    const int lane = threadIdx.x, seg = threadIdx.y, n_seg = blockDim.y, c = blockIdx.x * 32 + lane, s = blockIdx.y;
     const int first = a.seq_info[s], count = a.seq_info[a.n_seq + s], slot = a.seq_info[2 * a.n_seq + s], fresh = a.seq_info[3 * a.n_seq + s];
     if (count <= 0) return;
     const bool live = c < a.width;
-    const int n_seg = count >= 4 * MG_SEG ? MG_SEG : 1;
-    const int per = (count + n_seg - 1) / n_seg, t_lo = min(count, seg * per), t_hi = seg < n_seg ? min(count, t_lo + per) : t_lo;
     const float zb = (a.z_bias && live) ? a.z_bias[c] : 0.f, xb = (a.x_bias && live) ? a.x_bias[c] : 0.f;
     float *Sp = a.state + (int64_t)slot * a.slot_stride + c;
-    float S = (live && !fresh) ? *Sp : 0.f;
-    if (n_seg > 1) {
-        float A = 1.f, B = 0.f;
-        if (live) {
-            for (int t = t_lo; t < t_hi; t++) {
-                float z, cand;
-                mingru_gates(a, first + t, c, zb, xb, z, cand);
-                A *= 1.f - z; B = (1.f - z) * B + z * cand;
-            }
+    if (seg == 0) sS[lane] = (live && !fresh) ? *Sp : 0.f;
+    for (int base = 0; base < count; base += n_seg * MG_TPT) {
+        const int t_lo = base + seg * MG_TPT;
+        float z[MG_TPT], cand[MG_TPT], g[MG_TPT];
+#pragma unroll
+        for (int u = 0; u < MG_TPT; u++) {
+            const bool ok = live && t_lo + u < count;
+            const int64_t tok = first + t_lo + u;
+            z[u] = ok ? a.z[tok * a.z_stride + c] : 0.f;
+            cand[u] = ok ? a.x[tok * a.x_stride + c] : 0.f;
+            g[u] = (ok && a.g) ? a.g[tok * a.g_stride + c] : 0.f;
         }
-        sA[seg][threadIdx.x & 31] = A; sB[seg][threadIdx.x & 31] = B;
-        __syncthreads();
-        for (int j = 0; j < seg; j++) S = sA[j][threadIdx.x & 31] * S + sB[j][threadIdx.x & 31];
-    } else if (seg > 0) {
-        return;
+        float A = 1.f, B = 0.f;
+#pragma unroll
+        for (int u = 0; u < MG_TPT; u++) {
+            const bool ok = t_lo + u < count;
+            const float zz = ok ? sigmoidf_(z[u] + zb) : 0.f, uu = cand[u] + xb;  // a token beyond the end leaves the state as it is
+            z[u] = zz; cand[u] = uu >= 0.f ? uu + 0.5f : sigmoidf_(uu);
+            A *= 1.f - zz; B = (1.f - zz) * B + zz * cand[u];
+        }
+        sA[seg][lane] = A; sB[seg][lane] = B;
+        __syncthreads();  // (also: sS holds the state in front of this round)
+        float S = sS[lane];
+        for (int j = 0; j < seg; j++) S = sA[j][lane] * S + sB[j][lane];
+#pragma unroll
+        for (int u = 0; u < MG_TPT; u++) {
+            S = (1.f - z[u]) * S + z[u] * cand[u];
+            if (live && t_lo + u < count) a.dst[(int64_t)(first + t_lo + u) * a.dst_stride + c] = a.g ? S * silu_f(g[u]) : S;
+        }
+        __syncthreads();  // everybody has read sS, sA, sB
+        if (seg == n_seg - 1) sS[lane] = S;
     }
-    if (!live) return;
-    for (int t = t_lo; t < t_hi; t++) {
-        float z, cand;
-        mingru_gates(a, first + t, c, zb, xb, z, cand);
-        S = (1.f - z) * S + z * cand;
-        a.dst[(int64_t)(first + t) * a.dst_stride + c] = a.g ? S * silu_f(a.g[(int64_t)(first + t) * a.g_stride + c]) : S;
-    }
-    if (seg == n_seg - 1) *Sp = S;
+    __syncthreads();
+    if (seg == 0 && live) *Sp = sS[lane];
 }
 
 }  // namespace b200
@@ -222,7 +245,9 @@ extern "C" int b200_op_short_conv(const b200_short_conv_args *a, b200_stream_t s
     if (a->n_seq == 0 || a->n_tokens == 0) return B200_OK;
     const dim3 grid((unsigned)((a->channels + 127) / 128), (unsigned)((a->n_tokens + SC_TOK - 1) / SC_TOK), (unsigned)a->n_seq);
     OPX_REQUIRE(grid.y <= 65535, B200_ERR_UNSUPPORTED, "b200_op_short_conv: at most %d tokens in a batch", 65535 * SC_TOK);
-    short_conv_kernel<<<grid, 128, 0, (cudaStream_t)stream>>>(*a);
+    if (a->taps <= 4) short_conv_kernel<4><<<grid, 128, 0, (cudaStream_t)stream>>>(*a);
+    else if (a->taps <= 8) short_conv_kernel<8><<<grid, 128, 0, (cudaStream_t)stream>>>(*a);
+    else short_conv_kernel<0><<<grid, 128, 0, (cudaStream_t)stream>>>(*a);
     B200_CUDA_TRY(cudaGetLastError());
     return B200_OK;
 }
@@ -245,7 +270,10 @@ extern "C" int b200_op_mingru_scan(const b200_mingru_args *a, b200_stream_t stre
     OPX_REQUIRE(a->width > 0 && a->n_seq >= 0 && a->n_seq <= 65535 && a->slot_stride >= a->width, B200_ERR_INVALID, "b200_op_mingru_scan: bad sizes");
     if (a->n_seq == 0) return B200_OK;
     const dim3 grid((unsigned)((a->width + 31) / 32), (unsigned)a->n_seq);
-    mingru_scan_kernel<<<grid, 32 * MG_SEG, 0, (cudaStream_t)stream>>>(*a);
+    // stretches per CTA: as many as the longest sequence of the batch can fill (a sequence has at most n_tokens tokens)
+    int segs = (a->n_tokens + MG_TPT - 1) / MG_TPT;
+    segs = a->n_tokens <= 0 ? MG_SEG_MAX : segs < 1 ? 1 : segs > MG_SEG_MAX ? MG_SEG_MAX : segs;
+    mingru_scan_kernel<<<grid, dim3(32, (unsigned)segs), 0, (cudaStream_t)stream>>>(*a);
     B200_CUDA_TRY(cudaGetLastError());
     return B200_OK;
 }

@@ -67,7 +67,7 @@ def run_short_conv(u, w, bias, portions, taps, act, lead=2):
 
 
 @pytest.mark.parametrize("Cn,taps,portions,act", [(5, 4, [11], 0), (130, 4, [1, 1, 1, 2, 3, 40, 1], 1), (70, 2, [33, 2], 0), (9, 1, [4, 3], 1), (40, 7, [2, 2, 2, 70], 0),
-                                                  (300, 3, [64, 1, 32], 1)])
+                                                  (300, 3, [64, 1, 32], 1), (24, 11, [3, 30, 5, 1], 1), (24, 17, [40], 0)])
 def test_short_convolution_whole_and_in_portions(Cn, taps, portions, act):
     rng = np.random.default_rng(Cn + taps)
     T = sum(portions)
@@ -187,9 +187,9 @@ def test_head_norm_with_silu_gate(V, Hh, T):
 
 # ------------------------------------------------------------------------------------------------ sigmoid attention with a bias by distance
 def distance_table(rel_tab, pb, bias_max):
-    """[bias_max + 1, heads]: what the loader hands the kernel (computed here from the oracle's bucket function)."""
+    """[heads, bias_max + 1]: what the loader hands the kernel (computed here from the oracle's bucket function)."""
     B = rel_tab.shape[0]
-    return np.stack([rel_tab[R.distance_bucket(n, B, bias_max)] + pb for n in range(bias_max + 1)])
+    return np.ascontiguousarray(np.stack([rel_tab[R.distance_bucket(n, B, bias_max)] + pb for n in range(bias_max + 1)]).T)
 
 
 def run_sigmoid_attn(q, kc, vc, cell_seq, cell_pos, tok_seq, tok_pos, scale, G, table, bf16=0):
@@ -199,7 +199,7 @@ def run_sigmoid_attn(q, kc, vc, cell_seq, cell_pos, tok_seq, tok_pos, scale, G, 
     out = H.DeviceBuffer(4 * T * Hh * V + 256)
     a = SinkAttnArgs(q=bufs[0].ptr, q_stride=Hh * D, k_cache=bufs[1].ptr, k_cache_stride=kc.shape[1], v_cache=bufs[2].ptr, v_cache_stride=vc.shape[1], cell_seq=bufs[3].ptr,
                      cell_pos=bufs[4].ptr, tok_seq=bufs[5].ptr, tok_pos=bufs[6].ptr, sink=None, dst=out.ptr, dst_stride=Hh * V, n_head=Hh, n_head_kv=G, dim=D, vdim=V, n_tokens=T,
-                     n_kv=len(cell_seq), scale=scale, bf16_products=bf16, weights=1, dist_bias=bufs[7].ptr, n_dist=table.shape[0])
+                     n_kv=len(cell_seq), scale=scale, bf16_products=bf16, weights=1, dist_bias=bufs[7].ptr, n_dist=table.shape[1])
     need = int(lib().b200_sink_attn_workspace_bytes(C.byref(a)))  # > 0: few tokens and many cells, the cells are split over CTAs
     ws = H.DeviceBuffer(need + 256) if need else None
     check(lib().b200_op_sink_attn_ws(C.byref(a), ws.ptr if ws else None, need, None))
