@@ -63,11 +63,13 @@ __global__ void __launch_bounds__(128) short_conv_kernel(const b200_short_conv_a
 // ------------------------------------------------------------------------------------------------ gated delta rule
 // The columns of the state never interact: column j of S [dim, vdim] sees  S_j <- g S_j + k u_j  with  u_j = beta (v_j - g k.S_j),
 // and the read-out is  o_j = q.S_j(new) = g q.S_j(old) + (q.k) u_j,  so one pass over the old column gives both sums a token
-// needs.  A warp owns DR_CW columns of one (sequence, head); 8 lanes share a column, lane r of them keeping the rows
-// 4 (r + 8 i) .. + 3 in registers over the whole token loop, so a sum over a column is three exchanges among 8 lanes.
+// needs.  A warp owns DR_CW * DR_CPL columns of one (sequence, head); 8 lanes share DR_CPL columns, lane r of them keeping the rows
+// 4 (r + 8 i) .. + 3 of each in registers over the whole token loop, so a sum over a column is three exchanges among 8 lanes and
+// the q and k values a lane reads from shared memory serve DR_CPL columns (the loads, not the arithmetic, are what two CTAs on one
+// SM compete for).
 // The inputs of DR_CHUNK tokens are staged in shared memory: q and k as unit vectors (q scaled), q.k, the decay and beta once per
 // token; the next chunk's values travel to registers while the current chunk is worked on.
-constexpr int DR_CW = 4, DR_WARPS = 4, DR_COLS = DR_CW * DR_WARPS, DR_CHUNK = 16, DR_TPW = DR_CHUNK / DR_WARPS;
+constexpr int DR_CW = 4, DR_CPL = 1, DR_WARPS = 8, DR_COLS = DR_CW * DR_CPL * DR_WARPS, DR_CHUNK = 16, DR_TPW = DR_CHUNK / DR_WARPS;
 template <int DQ>  // float4 groups per lane: dim <= 32 DQ
 __global__ void __launch_bounds__(DR_WARPS * 32) delta_rule_scan_kernel(const b200_delta_rule_args a) {
     constexpr int DP = 32 * DQ;
@@ -78,13 +80,18 @@ __global__ void __launch_bounds__(DR_WARPS * 32) delta_rule_scan_kernel(const b2
     const int D = a.dim, V = a.vdim;
     const int first = a.seq_info[s], count = a.seq_info[a.n_seq + s], slot = a.seq_info[2 * a.n_seq + s], fresh = a.seq_info[3 * a.n_seq + s];
     if (count <= 0) return;
-    const int cb = blockIdx.x * DR_COLS, cw = lane >> 3, r = lane & 7, col = cb + warp * DR_CW + cw;
-    float *Sp = a.state + (int64_t)slot * a.slot_stride + ((int64_t)h * V + col) * D;
-    float S[DQ][4];
+    const int cb = blockIdx.x * DR_COLS, cw = lane >> 3, r = lane & 7, lc0 = warp * DR_CW * DR_CPL + cw;  // the lane's columns: cb + lc0 + DR_CW c
+    float *Sp = a.state + (int64_t)slot * a.slot_stride + ((int64_t)h * V + cb + lc0) * D;                // column c at Sp + DR_CW c D
+    float S[DR_CPL][DQ][4];
 #pragma unroll
-    for (int i = 0; i < DQ; i++)
+    for (int c = 0; c < DR_CPL; c++)
 #pragma unroll
-        for (int e = 0; e < 4; e++) { const int d = 4 * (r + 8 * i) + e; S[i][e] = (!fresh && d < D && col < V) ? Sp[d] : 0.f; }
+        for (int i = 0; i < DQ; i++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const int d = 4 * (r + 8 * i) + e;
+                S[c][i][e] = (!fresh && d < D && cb + lc0 + DR_CW * c < V) ? Sp[(int64_t)DR_CW * c * D + d] : 0.f;
+            }
     const float decay_rate = expf(a.a_log[h]), dtb = a.dt_bias ? a.dt_bias[h] : 0.f;
     // staging: the raw values of a chunk travel to registers (every thread a slice of the chunk), are parked in shared memory, and
     // warp w then turns the tokens w, w + DR_WARPS, ... into unit vectors in place
@@ -145,33 +152,49 @@ __global__ void __launch_bounds__(DR_WARPS * 32) delta_rule_scan_kernel(const b2
         }
         __syncthreads();
         if (t0 + DR_CHUNK < count) fetch(t0 + DR_CHUNK);
+        // unrolled so that the shared-memory loads of the following tokens are issued ahead of the chain S -> sums -> u -> S
+#pragma unroll 4
         for (int tt = 0; tt < nt; tt++) {
-            float ks0 = 0.f, ks1 = 0.f, qs0 = 0.f, qs1 = 0.f;
+            float ks[DR_CPL], qs[DR_CPL];
             float4 kv[DQ];
+#pragma unroll
+            for (int c = 0; c < DR_CPL; c++) ks[c] = qs[c] = 0.f;
 #pragma unroll
             for (int i = 0; i < DQ; i++) {
                 kv[i] = *reinterpret_cast<const float4 *>(&sk[tt][4 * (r + 8 * i)]);
                 const float4 qv = *reinterpret_cast<const float4 *>(&sq[tt][4 * (r + 8 * i)]);
-                ks0 += kv[i].x * S[i][0] + kv[i].z * S[i][2]; ks1 += kv[i].y * S[i][1] + kv[i].w * S[i][3];
-                qs0 += qv.x * S[i][0] + qv.z * S[i][2]; qs1 += qv.y * S[i][1] + qv.w * S[i][3];
-            }
-            float ks = ks0 + ks1, qs = qs0 + qs1;
 #pragma unroll
-            for (int off = 4; off >= 1; off >>= 1) { ks += __shfl_xor_sync(0xffffffffu, ks, off); qs += __shfl_xor_sync(0xffffffffu, qs, off); }
+                for (int c = 0; c < DR_CPL; c++) {
+                    ks[c] += (kv[i].x * S[c][i][0] + kv[i].z * S[c][i][2]) + (kv[i].y * S[c][i][1] + kv[i].w * S[c][i][3]);
+                    qs[c] += (qv.x * S[c][i][0] + qv.z * S[c][i][2]) + (qv.y * S[c][i][1] + qv.w * S[c][i][3]);
+                }
+            }
+#pragma unroll
+            for (int off = 4; off >= 1; off >>= 1)
+#pragma unroll
+                for (int c = 0; c < DR_CPL; c++) { ks[c] += __shfl_xor_sync(0xffffffffu, ks[c], off); qs[c] += __shfl_xor_sync(0xffffffffu, qs[c], off); }
             const float g = sg[tt];
-            const float u = sbeta[tt] * (sv[tt][warp * DR_CW + cw] - g * ks);
 #pragma unroll
-            for (int i = 0; i < DQ; i++) {
-                S[i][0] = g * S[i][0] + kv[i].x * u; S[i][1] = g * S[i][1] + kv[i].y * u;
-                S[i][2] = g * S[i][2] + kv[i].z * u; S[i][3] = g * S[i][3] + kv[i].w * u;
+            for (int c = 0; c < DR_CPL; c++) {
+                const float u = sbeta[tt] * (sv[tt][lc0 + DR_CW * c] - g * ks[c]);
+#pragma unroll
+                for (int i = 0; i < DQ; i++) {
+                    S[c][i][0] = g * S[c][i][0] + kv[i].x * u; S[c][i][1] = g * S[c][i][1] + kv[i].y * u;
+                    S[c][i][2] = g * S[c][i][2] + kv[i].z * u; S[c][i][3] = g * S[c][i][3] + kv[i].w * u;
+                }
+                if (r == 0 && cb + lc0 + DR_CW * c < V) a.dst[(int64_t)(first + t0 + tt) * a.dst_stride + (int64_t)h * V + cb + lc0 + DR_CW * c] = g * qs[c] + sqk[tt] * u;
             }
-            if (r == 0 && col < V) a.dst[(int64_t)(first + t0 + tt) * a.dst_stride + (int64_t)h * V + col] = g * qs + sqk[tt] * u;
         }
     }
 #pragma unroll
-    for (int i = 0; i < DQ; i++)
+    for (int c = 0; c < DR_CPL; c++)
 #pragma unroll
-        for (int e = 0; e < 4; e++) { const int d = 4 * (r + 8 * i) + e; if (d < D && col < V) Sp[d] = S[i][e]; }
+        for (int i = 0; i < DQ; i++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const int d = 4 * (r + 8 * i) + e;
+                if (d < D && cb + lc0 + DR_CW * c < V) Sp[(int64_t)DR_CW * c * D + d] = S[c][i][e];
+            }
 }
 
 template <int DQ>
