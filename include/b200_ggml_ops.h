@@ -144,6 +144,7 @@ enum b200_ext_op {
     B200_EXT_DELTA_RULE_SCAN = 19, /* src: q, k, v, a, b, a_log, dt_bias, seq_info, state; op_params: [2] heads, [3] kv_heads, [4] dim, [5] vdim, [6] q and k become
                                   unit vectors, [7] the eps of that, [8] q scale */
     B200_EXT_MINGRU_SCAN = 20, /* src: z, x, g (optional), z bias, x bias (optional), seq_info, state [width, slots] */
+    B200_EXT_NORM_PAIR = 21,   /* src: x1, w1, b1 (optional), x2, w2: dst = N(x1 + b1) * w1 + N(x2) * w2, N the RMS norm; op_params: [3] eps */
 };
 /* how attention turns scores into weights: SOFTMAX over the visible keys (with the sink in the denominator), or SIGMOID of every score by
  * itself with no normalisation over the keys (a sink has no meaning then) */
@@ -166,6 +167,11 @@ B200_API int b200_op_norm(const b200_tensor *x, const float *w, int64_t w_period
  * z sigmoid(z) (gate_on_output == 2). */
 B200_API int b200_op_norm_affine(const b200_tensor *x, const float *w, int64_t w_period, const float *bias, const b200_tensor *gate, const float *gate_bias,
                                  int gate_on_output, const b200_tensor *res, const b200_tensor *dst, float eps, int kind, b200_stream_t stream);
+
+/* Two results joined behind their own RMS norms, one row per block: dst = N(x1 + b1) * w1 + N(x2) * w2 with N(z) = z / sqrt(mean(z^2) + eps)
+ * over ne0; b1 optional; x1, x2, dst f32 rows of one shape with any row strides; ne0 <= 16384. */
+B200_API int b200_op_norm_pair(const b200_tensor *x1, const float *w1, const float *b1, const b200_tensor *x2, const float *w2, const b200_tensor *dst, float eps,
+                               b200_stream_t stream);
 
 /* PolyNorm: dst = c0 N(x) + c1 N(x^2) + c2 N(x^3) + c3 with N(z) = z / sqrt(mean(z^2) + eps) over ne0, powers element by
  * element; coef: 4 floats on the device. */

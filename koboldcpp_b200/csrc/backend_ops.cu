@@ -96,6 +96,9 @@ static bool ext_op_supported(const ggml_tensor *op) {
             return s[0] && s[0]->type == GGML_TYPE_F32 && op->type == GGML_TYPE_F32 && is_contiguous(s[0]) && is_contiguous(op);
         case B200_EXT_MUL_MAT_ID:
             return s[0] && s[1] && s[2] && (s[0]->type == GGML_TYPE_F32 || s[0]->type == GGML_TYPE_BF16) && f32_rows(s[1]) && s[2]->type == GGML_TYPE_I32 && f32_rows(op);
+        case B200_EXT_NORM_PAIR:
+            return f32_rows(s[0]) && f32_vec(s[1]) && (!s[2] || f32_vec(s[2])) && f32_rows(s[3]) && f32_vec(s[4]) && f32_rows(op) && same_shape(s[0], op) && same_shape(s[3], op) &&
+                   op->ne[0] <= 16384 && s[1]->ne[0] == op->ne[0] && s[4]->ne[0] == op->ne[0];
         case B200_EXT_ADD_SINUSOID:
             return f32_rows(s[0]) && f32_rows(op) && same_shape(s[0], op) && op->ne[2] == 1 && op->ne[3] == 1 && i32_vec(s[1]) && s[1]->ne[0] >= op->ne[1] && f32_vec(s[2]) &&
                    s[2]->ne[0] >= (op->ne[0] + 1) / 2;
@@ -302,6 +305,11 @@ static void run_ext(ExecCtx &x, const ggml_tensor *n) {
             }
             b200_tensor ta = as_b200(as), tb = as_b200(b), ti = as_b200(ids), td = as_b200(n);
             B200_CHECK_RC(b200_op_mul_mat_id_float(&ta, &tb, &ti, &td, x.stream));
+            break;
+        }
+        case B200_EXT_NORM_PAIR: {
+            b200_tensor a = as_b200(s[0]), c = as_b200(s[3]), d = as_b200(n);
+            B200_CHECK_RC(b200_op_norm_pair(&a, (const float *)s[1]->data, s[2] ? (const float *)s[2]->data : nullptr, &c, (const float *)s[4]->data, &d, ext_f(n, 3), x.stream));
             break;
         }
         case B200_EXT_ADD_SINUSOID: {

@@ -458,11 +458,17 @@ int md_build(b200_llama *m, const BatchShape &bs) {
             static const bool attn_f32 = getenv("B200_ATTN_F32") != nullptr;
             o->op_params[6] = L.proj1->type == GGML_TYPE_BF16 && !attn_f32;
             o->op_params[7] = (int32_t)V; o->op_params[8] = 0; o->op_params[9] = B200_ATTN_SIGMOID;
-            ggml_tensor *ya = b.binary(GGML_OP_ADD, b.mul_mat(L.wo, o), L.wo_bias);
+            ggml_tensor *ya = b.mul_mat(L.wo, o);
             ggml_tensor *s = b.alloc_result(GGML_TYPE_F32, lp.side_width, T);
             b.ext(s, B200_EXT_MINGRU_SCAN, {part(P, "mix.right.z"), part(P, "mix.right.x"), part(P, "mix.right.g"), L.zb, L.xb, seq_info, R.state});
             ggml_tensor *yg = b.mul_mat(L.wo_side, s);
-            y = norm(yg, L.out_r, nullptr, 0, norm(ya, L.out_l));
+            // the output bias of the attention side, both sides' norms, their weights (halved) and the sum: one launch
+            if (W <= 16384) {
+                y = b.ext(b.alloc_result(GGML_TYPE_F32, W, T), B200_EXT_NORM_PAIR, {ya, L.out_l, L.wo_bias, yg, L.out_r});
+                Builder::set_f(y, 3, eps);
+            } else {
+                y = norm(yg, L.out_r, nullptr, 0, norm(b.binary(GGML_OP_ADD, ya, L.wo_bias), L.out_l));
+            }
         }
         // where the layer's result goes: the first half of [x ; x0] when the next run starts a pass
         const bool next_starts = r + 1 < m->run_layer.size() && m->layer_hp[(size_t)m->run_layer[r + 1]].loop_input != 0;

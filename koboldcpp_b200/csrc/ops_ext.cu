@@ -197,6 +197,34 @@ __global__ void sigmoid_mul_kernel(TD a, TD b, TD dst, int64_t n) {
 
 static unsigned grid1d(int64_t n, int block) { return (unsigned)((n + block - 1) / block); }
 
+// two rows, each divided by its own root mean square and multiplied by its own weight, added: both rows wait in registers, the two
+// sums of squares share the block-wide exchange
+template <int VPT>
+__global__ void __launch_bounds__(1024) norm_pair_kernel(TD x1, const float *__restrict__ w1, const float *__restrict__ b1, TD x2, const float *__restrict__ w2, TD dst, float eps) {
+    __shared__ float sh[32];
+    const int64_t r = blockIdx.x;
+    const float *p1 = (const float *)row_ptr(x1, r), *p2 = (const float *)row_ptr(x2, r);
+    float *yr = (float *)row_ptr(dst, r);
+    const int n = (int)x1.ne[0];
+    float u[VPT], v[VPT], a[VPT], c[VPT], s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int k = 0; k < VPT; k++) {
+        const int i = threadIdx.x + k * blockDim.x;
+        u[k] = i < n ? p1[i] + (b1 ? b1[i] : 0.f) : 0.f;
+        v[k] = i < n ? p2[i] : 0.f;
+        a[k] = i < n ? w1[i] : 0.f;
+        c[k] = i < n ? w2[i] : 0.f;
+        s1 += u[k] * u[k]; s2 += v[k] * v[k];
+    }
+    s1 = block_sum(s1, sh); s2 = block_sum(s2, sh);
+    const float f1 = 1.0f / sqrtf(s1 / (float)n + eps), f2 = 1.0f / sqrtf(s2 / (float)n + eps);
+#pragma unroll
+    for (int k = 0; k < VPT; k++) {
+        const int i = threadIdx.x + k * blockDim.x;
+        if (i < n) yr[i] = u[k] * f1 * a[k] + v[k] * f2 * c[k];
+    }
+}
+
 // position vector of sines and cosines added to every row: a thread per pair (2i, 2i + 1), the angle pos * f_i in f32
 __global__ void add_sinusoid_kernel(TD x, const int32_t *__restrict__ pos, const float *__restrict__ freqs, TD dst, int64_t pairs, int64_t total) {
     const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -214,6 +242,22 @@ __global__ void add_sinusoid_kernel(TD x, const int32_t *__restrict__ pos, const
 
 using namespace b200;
 using namespace b200::opx;
+
+extern "C" int b200_op_norm_pair(const b200_tensor *x1, const float *w1, const float *b1, const b200_tensor *x2, const float *w2, const b200_tensor *dst, float eps,
+                                 b200_stream_t stream) {
+    OPX_REQUIRE(x1 && x2 && dst && w1 && w2 && x1->data && x2->data && dst->data, B200_ERR_INVALID, "b200_op_norm_pair: NULL argument");
+    OPX_REQUIRE(x1->type == B200_TYPE_F32 && x2->type == B200_TYPE_F32 && dst->type == B200_TYPE_F32 && x1->nb[0] == 4 && x2->nb[0] == 4 && dst->nb[0] == 4 && same_shape(x1, dst) &&
+                same_shape(x2, dst) && x1->ne[0] <= 16384, B200_ERR_UNSUPPORTED, "b200_op_norm_pair: f32 rows of one shape, at most 16384 values each");
+    const int64_t rows = nrows(dst);
+    if (rows == 0 || dst->ne[0] == 0) return B200_OK;
+    const int n = (int)dst->ne[0];
+    const int rb = n <= 256 ? 64 : n <= 1024 ? 128 : n <= 2048 ? 256 : n <= 4096 ? 512 : 1024, vpt = (n + rb - 1) / rb;
+#define B200_NP(V) norm_pair_kernel<V><<<(unsigned)rows, rb, 0, (cudaStream_t)stream>>>(td(x1), w1, b1, td(x2), w2, td(dst), eps)
+    if (vpt <= 4) B200_NP(4); else if (vpt <= 8) B200_NP(8); else B200_NP(16);
+#undef B200_NP
+    B200_CUDA_TRY(cudaGetLastError());
+    return B200_OK;
+}
 
 extern "C" int b200_op_add_sinusoid(const b200_tensor *x, const int32_t *pos, const float *freqs, const b200_tensor *dst, b200_stream_t stream) {
     OPX_REQUIRE(x && dst && pos && freqs && x->data && dst->data, B200_ERR_INVALID, "b200_op_add_sinusoid: NULL argument");

@@ -241,7 +241,7 @@ __global__ void __launch_bounds__(32 * MG_SEG_MAX) mingru_scan_kernel(const b200
             A *= 1.f - zz; B = (1.f - zz) * B + zz * cand[u];
         }
         sA[seg][lane] = A; sB[seg][lane] = B;
-        __syncthreads();  // (also: sS holds the state in front of this round)
+        __syncthreads();  // (also: sS holds the state in front of these stretches)
         float S = sS[lane];
         for (int j = 0; j < seg; j++) S = sA[j][lane] * S + sB[j][lane];
 #pragma unroll

@@ -222,6 +222,7 @@ _OPS_SIGS = {
     "b200_op_glu_scaled": (C.c_int, [C.c_int, C.POINTER(Tensor), C.POINTER(Tensor), C.POINTER(Tensor), C.POINTER(Tensor), C.c_float, C.c_float, C.c_void_p]),
     "b200_op_moe_combine_shared": (C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64,
                                              C.c_void_p, C.c_int64, C.c_float, C.c_void_p, C.c_int64, C.c_int64, C.c_int32, C.c_int64, C.c_void_p]),
+    "b200_op_norm_pair": (C.c_int, [C.POINTER(Tensor), C.c_void_p, C.c_void_p, C.POINTER(Tensor), C.c_void_p, C.POINTER(Tensor), C.c_float, C.c_void_p]),
     "b200_op_add_sinusoid": (C.c_int, [C.POINTER(Tensor), C.c_void_p, C.c_void_p, C.POINTER(Tensor), C.c_void_p]),
     "b200_op_short_conv": (C.c_int, [C.POINTER(ShortConvArgs), C.c_void_p]),
     "b200_op_delta_rule_scan": (C.c_int, [C.POINTER(DeltaRuleArgs), C.c_void_p]),

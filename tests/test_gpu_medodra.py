@@ -185,6 +185,19 @@ def test_head_norm_with_silu_gate(V, Hh, T):
     assert rel(dout.to_numpy(np.float32, (T, Hh, V)), R.rms_unit(x, eps) * w * R.silu(gate)) < 3e-6
 
 
+@pytest.mark.parametrize("n,T", [(40, 3), (70, 1), (1024, 4), (5000, 2)])
+def test_two_sides_joined_behind_their_norms(n, T):
+    """N(a + bias) * wa + N(b) * wb in one launch, the second input read from a wider row."""
+    rng = np.random.default_rng(n)
+    a, b2, bias, wa, wb, eps = rng.standard_normal((T, n)) * 4, rng.standard_normal((T, n + 6)), rng.standard_normal(n), rng.standard_normal(n), rng.standard_normal(n), 1e-5
+    da, db, dbias, dwa, dwb, dout = dev(a), dev(b2), dev(bias), dev(wa), dev(wb), H.DeviceBuffer(4 * T * n + 256)
+    ta, to = Tensor.contiguous(da.ptr, F32, (n, T)), Tensor.contiguous(dout.ptr, F32, (n, T))
+    tb = Tensor.contiguous(db.ptr + 8, F32, (n, T)); tb.nb[1] = 4 * (n + 6)
+    check(lib().b200_op_norm_pair(C.byref(ta), dwa.ptr, dbias.ptr, C.byref(tb), dwb.ptr, C.byref(to), eps, None))
+    want = R.rms_unit(a + bias, eps) * wa + R.rms_unit(b2[:, 2:2 + n], eps) * wb
+    assert rel(dout.to_numpy(np.float32, (T, n)), want) < 3e-6
+
+
 # ------------------------------------------------------------------------------------------------ sigmoid attention with a bias by distance
 def distance_table(rel_tab, pb, bias_max):
     """[heads, bias_max + 1]: what the loader hands the kernel (computed here from the oracle's bucket function)."""
