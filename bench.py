@@ -834,10 +834,10 @@ def medodra_config(size: str) -> dict:
     import math
     W, (h, g, d, v), (ne, top, ff, _ng, _nk), _window = GALIRAX_SIZES[size]
     mlp = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": ne, "top": top}, "shared": {"ff": ff}}
-    left = {"heads": h, "kv_heads": g, "dim": d, "vdim": v, "conv": 4, "bias_max": 2048, "q_temp": {"coef": 0.5, "every": 1024}, "scale": 1.0 / math.sqrt(d)}
+    left = {"heads": h, "kv_heads": g, "dim": d, "vdim": v, "conv": 4, "bias_max": 2048, "q_temp": {"coef": 0.25, "every": 1024}, "scale": 1.0 / math.sqrt(d)}
     par = {"type": "parallel", "mixer": {"left": left, "right": {"width": W}}, "mlp": mlp}
     delta = {"type": "delta", "mixer": {"heads": h, "kv_heads": g, "dim": d, "vdim": v, "conv": 4}, "mlp": mlp}
-    return {"architecture": "Medodra", "width": W, "vocab": DESIGN_VOCAB, "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0}, "residual_mult": 0.5,
+    return {"architecture": "Medodra", "width": W, "vocab": DESIGN_VOCAB, "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0}, "residual_mult": 0.7,
             "loop": {"start": 2, "stop": 4, "times": 1}, "layers": [par if il % 2 == 0 else delta for il in range(DESIGN_LAYERS)]}
 
 

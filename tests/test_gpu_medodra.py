@@ -346,7 +346,7 @@ from koboldcpp_b200.engine import Engine, Request  # noqa: E402
 CONFIGS = {
     # the looped stretch holds one layer of each kind; bias tables shorter than the prompts; 4 heads over 2 kv heads
     "looped": lambda: R.make_config([R.parallel_layer(), R.delta_layer(), R.parallel_layer(heads=2, kv_heads=2, dim=8, vdim=8, conv=2, bias_max=9, every=5, mlp=None),
-                                     R.delta_layer(heads=2, kv_heads=1, dim=8, vdim=12, conv=3)], loop=(1, 3, 3)),
+                                     R.delta_layer(heads=2, kv_heads=1, dim=8, vdim=12, conv=3)], loop=(1, 3, 4)),
     # a delta layer first and the loop from layer 0, run once; one head, one kv head, one expert per token and all experts per token, no
     # shared expert, a convolution of one tap and of six, dim != vdim, multipliers of exactly one, a width that is no multiple of 8
     "odd": lambda: R.make_config([R.delta_layer(heads=1, kv_heads=1, dim=24, vdim=40, conv=1, mlp=R.moe_cfg(ff=40, experts=5, top=1, shared=0)),

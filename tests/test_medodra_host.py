@@ -27,8 +27,8 @@ def test_layer_parameters_from_the_configuration():
 
 
 def test_run_order_of_a_looped_stretch():
-    assert run_order(5, {"start": 1, "stop": 3, "times": 3}) == [0, 1, 2, 1, 2, 1, 2, 3, 4]
-    assert [il for il, _ in R.run_order(R.make_config([0] * 5, loop=(1, 3, 3)))] == [0, 1, 2, 1, 2, 1, 2, 3, 4]
+    assert run_order(5, {"start": 2, "stop": 4, "times": 3}) == [0, 1, 2, 3, 2, 3, 2, 3, 4]
+    assert [il for il, _ in R.run_order(R.make_config([0] * 5, loop=(2, 4, 3)))] == [0, 1, 2, 3, 2, 3, 2, 3, 4]
     assert [s for _, s in R.run_order(R.make_config([0] * 3, loop=(0, 2, 2)))] == [True, False, True, False, False]
     assert R.run_order(R.make_config([0] * 2)) == [(0, False), (1, False)]
 
